@@ -1,7 +1,8 @@
 """The one registry from an architecture's name (``architectures[0]`` of
 config.json) to its typed configuration class.  The reference routes its
 supported names through one list (convert.py:15-19, 31); here each name maps
-to a class with ``from_dict(config_json) -> cfg`` and ``cfg.to_spec()``.
+to a class with ``from_dict(config_json) -> cfg`` and ``cfg.to_spec()``.  The name is
+``architectures[0]``, or the string under ``architecture`` where a design writes that.
 """
 from __future__ import annotations
 
@@ -9,6 +10,7 @@ import json
 import os
 from typing import Any, Dict
 
+from .golulix import GolulixConfig
 from .llama import ConfigError, LlamaConfig
 
 _ARCHITECTURES: Dict[str, Any] = {}
@@ -26,8 +28,10 @@ def architectures() -> Dict[str, Any]:
 
 def config_from_dict(d: Dict[str, Any]) -> Any:
     archs = d.get("architectures")
+    if not archs and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]           # some designs name themselves under this key
     if not archs:
-        raise ConfigError("config.json has no 'architectures' entry")
+        raise ConfigError("config.json has no 'architectures' (or 'architecture') entry")
     name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(
@@ -45,3 +49,4 @@ def load_config(model_dir: str) -> Any:
 
 register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("MistralForCausalLM", LlamaConfig)
+register_architecture("Golulix", GolulixConfig)

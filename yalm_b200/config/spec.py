@@ -50,10 +50,13 @@ class RunEntry:
     """One execution of a layer inside a step.  ``layer`` indexes
     ``ModelSpec.layers``; the same layer may appear in several entries.
     ``reads_cache_of`` names an earlier entry (by its index in the run order)
-    whose cache this entry reads instead of owning one."""
+    whose cache this entry reads instead of owning one.  ``adds_embedding``: the
+    embedding's output (the residual stream as it was before the first entry) is added
+    to the stream right before this entry runs."""
 
     layer: int
     reads_cache_of: Optional[int] = None
+    adds_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -69,6 +72,9 @@ class ModelSpec:
     head: PartSpec
     stop_token_ids: List[int] = field(default_factory=list)
     bos_token_id: Optional[int] = None
+    # the context when the caller names none (a design without a largest position
+    # has no natural one); None: max_positions
+    default_context: Optional[int] = None
 
     def validate(self) -> None:
         if not self.layers:

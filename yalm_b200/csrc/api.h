@@ -25,6 +25,11 @@ int yalm_rmsnorm(float* x, const float* partials, int n_partials, long long part
 int yalm_silu_mul(const float* gu, int n_partials, long long partial_stride, void* out,
                   int out_dtype, int rows, int F, int paired, cudaStream_t stream);
 
+// `window` and `scale`, wherever an attention function takes them: window > 0, a query sees
+// the last `window` positions; window < 0, the positions of its own chunk of -window
+// positions (chunks counted from position 0 of the sequence); 0, every earlier position.
+// scale multiplies q.k; scale <= 0 stands for 1 / sqrt(hd).
+//
 // The cache of a layer run, wherever it is an argument: contiguous per sequence,
 // [slots][G][capacity][hd] (page_table null), or pages of 64 positions,
 // [pages][G][64][hd], with page_table [slots][pages_per_slot] naming the page of rows
@@ -50,13 +55,13 @@ int yalm_advance(const int* q_start, const int* seq_slot, int* slot_pos, int n_s
 int yalm_attention(const void* q, const void* kv_step, const void* k_cache, const void* v_cache,
                    const int* token_seq, const int* q_start, const int* seq_slot,
                    const int* slot_pos, void* out, float* part_o, float* part_ml, int dtype,
-                   int n_tokens, int H, int G, int hd, int capacity, int window, int nsplit,
+                   int n_tokens, int H, int G, int hd, int capacity, int window, float scale, int nsplit,
                    const int* page_table, int pages_per_slot, int n_pages, cudaStream_t stream);
 
 int yalm_attention_decode(const void* q, const void* k_cache, const void* v_cache,
                           const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                           float* part_ml, int* counters, int* status, int dtype, int n_seqs, int H,
-                          int G, int hd, int capacity, int window, int chunk, int max_context,
+                          int G, int hd, int capacity, int window, float scale, int chunk, int max_context,
                           const int* page_table, int pages_per_slot, int n_pages, cudaStream_t stream);
 
 // 16-bit attention on tensor cores (attention_mma_prefill.cu, attention_mma.cu; dtype 1 or 2): head sizes in steps of
@@ -64,12 +69,12 @@ int yalm_attention_decode(const void* q, const void* k_cache, const void* v_cach
 int yalm_attention_prefill_mma(const void* q, const void* kv_step, const void* k_cache,
                                const void* v_cache, const int* q_start, const int* seq_slot,
                                const int* slot_pos, void* out, int dtype, int n_seqs,
-                               int max_q_len, int H, int G, int hd, int capacity, int window,
+                               int max_q_len, int H, int G, int hd, int capacity, int window, float scale,
                                const int* page_table, int pages_per_slot, int n_pages, cudaStream_t stream);
 int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                               const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                               float* part_ml, int* counters, int* status, int dtype, int n_seqs,
-                              int H, int G, int hd, int capacity, int window, int max_context,
+                              int H, int G, int hd, int capacity, int window, float scale, int max_context,
                               int chunks_per_block, int warps, const int* page_table, int pages_per_slot,
                               int n_pages, cudaStream_t stream);
 // ... compiled with two warps per block (attention_mma_two_warps.cu); yalm_attention_decode_mma
@@ -77,7 +82,7 @@ int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_
 int yalm_attention_decode_mma_two_warps(const void* q, const void* k_cache, const void* v_cache,
                                         const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                                         float* part_ml, int* counters, int* status, int dtype, int n_seqs,
-                                        int H, int G, int hd, int capacity, int window, int max_context,
+                                        int H, int G, int hd, int capacity, int window, float scale, int max_context,
                                         int chunks_per_block, const int* page_table, int pages_per_slot,
                                         int n_pages, cudaStream_t stream);
 // ... with the rotary kernel's work inside (attention_mma_fused.cu): takes this step's q/k/v product
@@ -86,7 +91,7 @@ int yalm_attention_decode_mma_fused(const float* qkv, int n_partials, long long 
                                     const float* cos_sin, void* k_cache, void* v_cache,
                                     const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                                     float* part_ml, int* counters, int* status, int dtype, int n_seqs,
-                                    int H, int G, int hd, int capacity, int window, int max_context,
+                                    int H, int G, int hd, int capacity, int window, float scale, int max_context,
                                     int chunks_per_block, const int* page_table, int pages_per_slot,
                                     int n_pages, cudaStream_t stream);
 
@@ -94,13 +99,13 @@ int yalm_attention_decode_mma_fused(const float* qkv, int n_partials, long long 
 // at their first token, head size 64 or 128
 int yalm_attention_prefill_tc(const void* q, const void* kv_step, const int* q_start, void* out,
                               int dtype, int n_tokens, int n_seqs, int max_q_len, int H, int G,
-                              int hd, int window, int* status, cudaStream_t stream);
+                              int hd, int window, float scale, int* status, cudaStream_t stream);
 // ... for sequences that go on from slot_pos, no one wrapping around its ring in this step:
 // every key (this step's too) from the layer's cache, paged or one block per sequence
 int yalm_attention_prefill_tc_cache(const void* q, const void* k_cache, const void* v_cache,
                                     const int* q_start, const int* seq_slot, const int* slot_pos,
                                     void* out, int dtype, int n_tokens, int n_seqs, int max_q_len,
-                                    int n_slots, int H, int G, int hd, int capacity, int window,
+                                    int n_slots, int H, int G, int hd, int capacity, int window, float scale,
                                     const int* page_table, int pages_per_slot, int n_pages, int* status,
                                     cudaStream_t stream);
 
@@ -161,6 +166,41 @@ int yalm_gemm_2sm_token_tile(int M, int N, int splits);
 // (head sizes that divide 128).
 int yalm_gemm_2sm_rope(const void* A, const void* W, int ab_dtype, int M, int N, int K,
                        const yalm_rope_args* rope, int* status, cudaStream_t stream);
+
+// ---- small_ops.cu ---------------------------------------------------------------------
+// x[t] = E[token t] + P[row t] (also into x_copy when given): row = buckets for a sequence's
+// position 0, else (previous token * mul_prev + token * mul_cur) mod buckets.  prev_token
+// [slots] holds the last token each sequence has been given; the kernel keeps it up to date.
+int yalm_embed_pair(const int* tokens, const int* token_seq, const int* q_start, const int* seq_slot,
+                    const int* slot_pos, const void* table, const void* pair_table, int table_dtype,
+                    int* prev_token, float* x, float* x_copy, int n_tokens, int dim, int vocab,
+                    int buckets, long long mul_prev, long long mul_cur, int* status,
+                    cudaStream_t stream);
+// o [n, H, hd] *= sigmoid(sum of the n_partials slices of g [n, H])
+int yalm_head_gate(void* o, int dtype, const float* g, int n_partials, long long partial_stride,
+                   int n_tokens, int H, int hd, cudaStream_t stream);
+// v <- cap * tanh(v / cap) over n floats
+int yalm_softcap(float* v, long long n, float cap, cudaStream_t stream);
+// x += y + sum of n_partials slices, n floats each
+int yalm_residual_add(float* x, const float* y, const float* partials, int n_partials,
+                      long long partial_stride, long long n, cudaStream_t stream);
+
+// ---- routed.cu: a routed feed-forward ----------------------------------------------------
+int yalm_route_topk(const float* z, int n_partials, long long partial_stride, int n_tokens, int E,
+                    int n_groups, int keep, int top, int renormalise, int* choice, float* weight,
+                    int* counts, cudaStream_t stream);
+int yalm_route_plan(int* counts, const int* choice, int n_pairs, int top, int E, int tile_rows,
+                    int* first_row, int* pair_row, int* row_token, int* tile_expert, int* tile_row0,
+                    int* n_tiles, cudaStream_t stream);
+int yalm_gather_rows(const void* src, const int* row_token, void* dst, int dtype, int rows, int dim,
+                     cudaStream_t stream);
+int yalm_gemm_grouped(const void* A, int a_dtype, const void* W, int w_dtype, void* out, int out_dtype,
+                      const int* first_row, const int* tile_expert, const int* tile_row0,
+                      const int* n_tiles, int max_tiles, int N, int K, cudaStream_t stream);
+int yalm_glu_clamp(const float* gu, int n_partials, long long partial_stride, void* out, int out_dtype,
+                   long long rows, int F, float alpha, float limit, float shift, cudaStream_t stream);
+int yalm_routed_combine(float* x, const float* y, const int* pair_row, const float* weight,
+                        int n_tokens, int top, int dim, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

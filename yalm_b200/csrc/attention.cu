@@ -115,7 +115,7 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
   const int past = slot_pos[slot];
   const int qs = q_start[b];
   const int pos = past + (t - qs);
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = first_visible(pos, window);
   const int nkeys = pos - lo + 1;
   const int per = (nkeys + nsplit - 1) / nsplit;
   const int s_lo = lo + split * per;
@@ -321,7 +321,7 @@ attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
 
   const int slot = seq_slot[t];
   const int pos = slot_pos[slot];                           // the query's position
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = first_visible(pos, window);
   const int nkeys = pos - lo + 1;
   const int n_active = (nkeys + chunk - 1) / chunk;
   if (n_active > max_chunks && c == 0 && threadIdx.x == 0) atomicOr(status, ERR_CONTEXT_RANGE);
@@ -549,12 +549,12 @@ static int launch_attention(const void* q, const void* kv_step, const void* k_ca
                             const void* v_cache, const int* token_seq, const int* q_start,
                             const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                             float* part_ml, int n_tokens, int H, int G, int hd, int capacity,
-                            int window, int nsplit, const int* page_table, int pps, int n_pages,
-                            cudaStream_t stream) {
+                            int window, float scale_in, int nsplit, const int* page_table, int pps,
+                            int n_pages, cudaStream_t stream) {
   const int R = H / G;
   const int nchunks = (R + ATT_RT - 1) / ATT_RT;
   const dim3 block(ATT_WARPS * 32);
-  const float scale = 1.0f / sqrtf((float)hd);
+  const float scale = score_scale(scale_in, hd);
   // gridDim.z is limited to 65535: tokens run in slices
   for (int t0 = 0; t0 < n_tokens; t0 += 65535) {
   const dim3 grid(nsplit, G * nchunks, n_tokens - t0 < 65535 ? n_tokens - t0 : 65535);
@@ -590,8 +590,9 @@ extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_
                               const void* v_cache, const int* token_seq, const int* q_start,
                               const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                               float* part_ml, int dtype, int n_tokens, int H, int G, int hd,
-                              int capacity, int window, int nsplit, const int* page_table,
-                              int pages_per_slot, int n_pages, cudaStream_t stream) {
+                              int capacity, int window, float scale, int nsplit,
+                              const int* page_table, int pages_per_slot, int n_pages,
+                              cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd % 8 != 0 || hd > 256 || hd <= 0) return -2;     // head sizes: multiples of 8 up to 256
   if (G <= 0 || H % G != 0) return -3;
@@ -600,15 +601,15 @@ extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_
   if (dtype == DT_F32)
     return launch_attention<float>(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot,
                                    slot_pos, out, part_o, part_ml, n_tokens, H, G, hd, capacity,
-                                   window, nsplit, page_table, pages_per_slot, n_pages, stream);
+                                   window, scale, nsplit, page_table, pages_per_slot, n_pages, stream);
   if (dtype == DT_F16)
     return launch_attention<__half>(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot,
                                     slot_pos, out, part_o, part_ml, n_tokens, H, G, hd, capacity,
-                                    window, nsplit, page_table, pages_per_slot, n_pages, stream);
+                                    window, scale, nsplit, page_table, pages_per_slot, n_pages, stream);
   if (dtype != DT_BF16) return -3;
   return launch_attention<__nv_bfloat16>(q, kv_step, k_cache, v_cache, token_seq, q_start,
                                          seq_slot, slot_pos, out, part_o, part_ml, n_tokens, H, G,
-                                         hd, capacity, window, nsplit, page_table, pages_per_slot, n_pages,
+                                         hd, capacity, window, scale, nsplit, page_table, pages_per_slot, n_pages,
                                          stream);
 }
 
@@ -622,7 +623,7 @@ extern "C" int yalm_attention_decode(const void* q, const void* k_cache, const v
                                      const int* seq_slot, const int* slot_pos, void* out,
                                      float* part_o, float* part_ml, int* counters, int* status,
                                      int dtype, int n_seqs, int H, int G, int hd, int capacity,
-                                     int window, int chunk, int max_context,
+                                     int window, float scale_in, int chunk, int max_context,
                                      const int* page_table, int pages_per_slot, int n_pages,
                                      cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
@@ -637,11 +638,11 @@ extern "C" int yalm_attention_decode(const void* q, const void* k_cache, const v
   const int R = H / G;
   const int nchunks = (R + ATT_RT - 1) / ATT_RT;
   if ((size_t)G * nchunks > 65535) return -4;
-  const int visible = window > 0 && window < max_context ? window : max_context;
+  const int visible = most_visible(max_context, window);
   const int max_chunks = (visible + chunk - 1) / chunk;
   const dim3 grid(max_chunks, G * nchunks, n_seqs);
   const dim3 block(ATT_WARPS * 32);
-  const float scale = 1.0f / sqrtf((float)hd);
+  const float scale = score_scale(scale_in, hd);
 #define YALM_DEC_CASE(T, LPK)                                                                  \
   do {                                                                                         \
     static size_t attr_smem = 0;                                                               \
@@ -744,6 +745,6 @@ extern "C" int yalm_attention_no_alloc(const void* q, const void* kv_step, const
   float* part_o = base;                                              // [tokens, H, nsplit, hd]
   float* part_ml = base + (size_t)n_tokens * H * nsplit * hd;        // [tokens, H, nsplit, 2]
   return yalm_attention(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot, slot_pos, out,
-                        part_o, part_ml, dtype, n_tokens, H, G, hd, capacity, window, nsplit,
+                        part_o, part_ml, dtype, n_tokens, H, G, hd, capacity, window, 0.f, nsplit,
                         nullptr, 0, 0, stream);            // a contiguous cache only
 }

@@ -17,17 +17,17 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
                                          const int* seq_slot, const int* slot_pos, void* out,
                                          float* part_o, float* part_ml, int* counters, int* status,
                                          int dtype, int n_seqs, int H, int G, int hd, int capacity,
-                                         int window, int max_context, int chunks_per_block,
+                                         int window, float scale, int max_context, int chunks_per_block,
                                          int warps, const int* page_table, int pages_per_slot,
                                          int n_pages, cudaStream_t stream) {
   if (warps == 2)                     // compiled in a translation unit of its own
     return yalm_attention_decode_mma_two_warps(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o,
                                                part_ml, counters, status, dtype, n_seqs, H, G, hd,
-                                               capacity, window, max_context, chunks_per_block,
+                                               capacity, window, scale, max_context, chunks_per_block,
                                                page_table, pages_per_slot, n_pages, stream);
   if (warps != FD_WARPS_MAX) return -4;
   return decode_mma_dispatch<false, FD_WARPS_MAX>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o,
                                                   part_ml, counters, status, dtype, n_seqs, H, G, hd,
-                                                  capacity, window, max_context, chunks_per_block,
+                                                  capacity, window, scale, max_context, chunks_per_block,
                                                   page_table, pages_per_slot, n_pages, nullptr, stream);
 }

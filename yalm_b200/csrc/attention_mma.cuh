@@ -112,7 +112,7 @@ __device__ __forceinline__ void load_strided_tile(uint32_t base, int rows, int n
 
 // ----------------------------------------------------------------- prefill
 // grid (query tiles of a sequence, heads, sequences); a block takes 64 query
-// tokens of one head.  scale_log2 = log2(e) / sqrt(hd).
+// tokens of one head.  scale_log2 = log2(e) * the scores' scale (1 / sqrt(hd) unless given).
 template <int HDP, typename T16>
 __global__ void __launch_bounds__(FP_THREADS, 2)
 attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_step,
@@ -146,7 +146,7 @@ attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_st
   // the visible key range of the whole tile: [k_begin, k_end)
   const int p_first = past + m0, p_last = past + m0 + rows - 1;
   const int k_end = p_last + 1;
-  const int k_begin = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int k_begin = first_visible(p_first, window);
   const int kb0 = k_begin / FA_BN, kb1 = (k_end + FA_BN - 1) / FA_BN;
 
   const size_t step_row = (size_t)2 * G * hd;
@@ -189,6 +189,7 @@ attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_st
     for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int p_row[2] = {past + m0 + warp * 16 + gid, past + m0 + warp * 16 + gid + 8};
+  const int lo_row[2] = {first_visible(p_row[0], window), first_visible(p_row[1], window)};
   const int w_first = past + m0 + warp * 16, w_last = w_first + 15;
   const int q_row = warp * 16 + (lane & 15);
 
@@ -226,7 +227,7 @@ attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_st
       }
       // mask and online softmax (rows gid and gid + 8 of this warp)
       float m_new[2] = {m_run[0], m_run[1]};
-      const bool inside = j_base + 31 <= w_first && (window <= 0 || j_base > w_last - window);
+      const bool inside = j_base + 31 <= w_first && j_base >= first_visible(w_last, window);
       if (inside) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -242,7 +243,7 @@ attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_st
           for (int j = 0; j < 4; ++j) {
             const int key = j_base + i * 8 + tig * 2 + (j & 1);
             const int pr = p_row[j >> 1];
-            const bool vis = key <= pr && (window <= 0 || key > pr - window);
+            const bool vis = key <= pr && key >= lo_row[j >> 1];
             s[i][j] = vis ? s[i][j] * scale_log2 : -INFINITY;
             m_new[j >> 1] = fmaxf(m_new[j >> 1], s[i][j]);
           }
@@ -454,7 +455,7 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   // Positions are written by the advance kernel alone, and that kernel lets nothing start
   // before it has ended: they too may be read while the previous kernel still runs.
   const int pos = slot_pos[slot];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = first_visible(pos, window);
   const int nkeys = pos - lo + 1;
   const int n_chunks = (nkeys + FD_CHUNK - 1) / FD_CHUNK;
   const int n_parts = (n_chunks + cpc - 1) / cpc;
@@ -919,7 +920,7 @@ template <int HDP, int NT, typename T16, bool PAGED, bool FUSED, int NW>
 static int launch_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
-                             int hd, int capacity, int window, int cpc, int max_parts,
+                             int hd, int capacity, int window, float scale, int cpc, int max_parts,
                              const int* page_table, int pps, int n_pages, const fd_fused_args& fz,
                              cudaStream_t stream) {
   // Q, then every warp's ring of (K, V) stages; the merge buffer lies over them
@@ -935,7 +936,7 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
   }
   const int nhc = (H / G + FD_ROWS - 1) / FD_ROWS;
   const dim3 grid(max_parts, G * nhc, n_seqs);
-  const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  const float scale_log2 = 1.4426950408889634f * score_scale(scale, hd);
   launch_pdl(attn_decode_mma_kernel<HDP, NT, T16, PAGED, FUSED, NW>, grid, dim3(NW * 32), smem, stream,
              (const T16*)q, (const T16*)k_cache, (const T16*)v_cache,
              seq_slot, slot_pos, (T16*)out, part_o, part_ml, counters, status, H, G, hd,
@@ -948,7 +949,7 @@ template <int HDP, typename T16>
 static int launch_prefill(const void* q, const void* kv_step, const void* k_cache,
                           const void* v_cache, const int* q_start, const int* seq_slot,
                           const int* slot_pos, void* out, int n_seqs, int max_q_len, int H, int G,
-                          int hd, int capacity, int window, const int* page_table, int pps,
+                          int hd, int capacity, int window, float scale, const int* page_table, int pps,
                           int n_pages, cudaStream_t stream) {
   const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * HDP * 2;
   static bool attr_set = false;
@@ -963,7 +964,7 @@ static int launch_prefill(const void* q, const void* kv_step, const void* k_cach
     attr_set = true;
   }
   const dim3 grid((max_q_len + FA_BM - 1) / FA_BM, H, n_seqs);
-  const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  const float scale_log2 = 1.4426950408889634f * score_scale(scale, hd);
   launch_pdl(attn_prefill_mma_kernel<HDP, T16>, grid, dim3(FP_THREADS), smem, stream,
              (const T16*)q, (const T16*)kv_step, (const T16*)k_cache,
              (const T16*)v_cache, q_start, seq_slot, slot_pos, (T16*)out, H, G,
@@ -977,7 +978,7 @@ template <bool FUSED, int NW>
 static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v_cache,
                                const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                                float* part_ml, int* counters, int* status, int dtype, int n_seqs, int H,
-                               int G, int hd, int capacity, int window, int max_context,
+                               int G, int hd, int capacity, int window, float scale, int max_context,
                                int chunks_per_block, const int* page_table,
                                int pages_per_slot, int n_pages, const fd_fused_args* fused,
                                cudaStream_t stream) {
@@ -987,7 +988,7 @@ static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v
   if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
   if (G <= 0 || H % G != 0) return -3;
   if (max_context <= 0 || n_seqs > 65535 || chunks_per_block < 1) return -4;
-  const int visible = window > 0 && window < max_context ? window : max_context;
+  const int visible = most_visible(max_context, window);
   const int max_chunks = (visible + FD_CHUNK - 1) / FD_CHUNK;
   const int max_parts = (max_chunks + chunks_per_block - 1) / chunks_per_block;
   if ((size_t)G * ((H / G + FD_ROWS - 1) / FD_ROWS) > 65535) return -4;
@@ -997,7 +998,7 @@ static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v
 #define YALM_FD_(HDP, NT, T, PAGED)                                                              \
   launch_decode_mma<HDP, NT, T, PAGED, FUSED, NW>(q, k_cache, v_cache, seq_slot, slot_pos, out,  \
                                                   part_o, part_ml, counters, status, n_seqs, H,  \
-                                                  G, hd, capacity, window, chunks_per_block,     \
+                                                  G, hd, capacity, window, scale, chunks_per_block, \
                                                   max_parts, page_table, pages_per_slot,         \
                                                   n_pages, fz, stream)
 #define YALM_FD(HDP, NT, T) (page_table ? YALM_FD_(HDP, NT, T, true) : YALM_FD_(HDP, NT, T, false))

@@ -13,7 +13,7 @@ extern "C" int yalm_attention_decode_mma_fused(const float* qkv, int n_partials,
                                                const int* seq_slot, const int* slot_pos, void* out,
                                                float* part_o, float* part_ml, int* counters,
                                                int* status, int dtype, int n_seqs, int H, int G, int hd,
-                                               int capacity, int window, int max_context,
+                                               int capacity, int window, float scale, int max_context,
                                                int chunks_per_block, const int* page_table,
                                                int pages_per_slot, int n_pages, cudaStream_t stream) {
   if (qkv == nullptr || cos_sin == nullptr || n_partials < 1) return -3;
@@ -21,6 +21,6 @@ extern "C" int yalm_attention_decode_mma_fused(const float* qkv, int n_partials,
   const fd_fused_args fz = {qkv, reinterpret_cast<const float2*>(cos_sin), partial_stride, n_partials};
   return decode_mma_dispatch<true, FD_WARPS_MAX>(nullptr, k_cache, v_cache, seq_slot, slot_pos, out, part_o,
                                                  part_ml, counters, status, dtype, n_seqs, H, G, hd, capacity,
-                                                 window, max_context, chunks_per_block, page_table,
+                                                 window, scale, max_context, chunks_per_block, page_table,
                                                  pages_per_slot, n_pages, &fz, stream);
 }

@@ -11,7 +11,7 @@ extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, co
                                           const void* v_cache, const int* q_start,
                                           const int* seq_slot, const int* slot_pos, void* out,
                                           int dtype, int n_seqs, int max_q_len, int H, int G,
-                                          int hd, int capacity, int window, const int* page_table,
+                                          int hd, int capacity, int window, float scale, const int* page_table,
                                           int pages_per_slot, int n_pages, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
@@ -20,7 +20,7 @@ extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, co
   if (H > 65535 || n_seqs > 65535) return -4;
 #define YALM_FP(HDP, T)                                                                          \
   return launch_prefill<HDP, T>(q, kv_step, k_cache, v_cache, q_start, seq_slot, slot_pos, out,  \
-                                n_seqs, max_q_len, H, G, hd, capacity, window, page_table,        \
+                                n_seqs, max_q_len, H, G, hd, capacity, window, scale, page_table, \
                                 pages_per_slot, n_pages, stream)
   if (dtype == DT_F16) {
     if (hd <= 64) YALM_FP(64, __half);

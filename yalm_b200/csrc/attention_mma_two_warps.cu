@@ -9,11 +9,11 @@ extern "C" int yalm_attention_decode_mma_two_warps(const void* q, const void* k_
                                                    const int* seq_slot, const int* slot_pos, void* out,
                                                    float* part_o, float* part_ml, int* counters,
                                                    int* status, int dtype, int n_seqs, int H, int G, int hd,
-                                                   int capacity, int window, int max_context,
+                                                   int capacity, int window, float scale, int max_context,
                                                    int chunks_per_block, const int* page_table,
                                                    int pages_per_slot, int n_pages, cudaStream_t stream) {
   return decode_mma_dispatch<false, 2>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
-                                       counters, status, dtype, n_seqs, H, G, hd, capacity, window,
+                                       counters, status, dtype, n_seqs, H, G, hd, capacity, window, scale,
                                        max_context, chunks_per_block, page_table, pages_per_slot, n_pages,
                                        nullptr, stream);
 }

@@ -233,7 +233,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     t_m0[x] = m0 + x * TA_BM;
     t_rows[x] = max(0, min(TA_BM, q_len - t_m0[x]));
     const int k_end = past + t_m0[x] + t_rows[x];
-    const int k_begin = window > 0 ? max(0, past + t_m0[x] - window + 1) : 0;
+    const int k_begin = first_visible(past + t_m0[x], window);
     t_kb0[x] = k_begin / TA_BN;
     t_kb1[x] = t_rows[x] > 0 ? (k_end + TA_BN - 1) / TA_BN : t_kb0[x];
   }
@@ -422,6 +422,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int my_kb0 = x ? t_kb0[1] : t_kb0[0], my_kb1 = x ? t_kb1[1] : t_kb1[0];
     const int p = past + my_m0 + row;                         // this row's position
     const int p_hi = past + my_m0 + TA_BM - 1;
+    const int p_lo = first_visible(p, window);                // the first key this row sees
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t my_s = (x ? tmem_s[1] : tmem_s[0]) + lane_addr;
     const uint32_t my_o = (x ? tmem_o[1] : tmem_o[0]) + lane_addr;
@@ -450,12 +451,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int i = 0; i < TA_BN; ++i) s[i] = __uint_as_float(raw[i]);
       }
       // every row of the tile sees every key of the block?
-      const bool inside = j0 + TA_BN - 1 <= past + my_m0 && (window <= 0 || j0 > p_hi - window);
+      const bool inside = j0 + TA_BN - 1 <= past + my_m0 && j0 >= first_visible(p_hi, window);
       if (!inside) {
 #pragma unroll
         for (int i = 0; i < TA_BN; ++i) {
           const int key = j0 + i;
-          const bool vis = key <= p && (window <= 0 || key > p - window);
+          const bool vis = key <= p && key >= p_lo;
           s[i] = vis ? s[i] : -INFINITY;
         }
       }
@@ -580,7 +581,7 @@ template <int HD, typename T16>
 static int launch_prefill_tc(const void* q, const void* k_rows, const void* v_rows, long long kv_n_rows,
                              long long kv_cols, const ta_cache_args& ca, const int* q_start, void* out,
                              int n_tokens, int n_seqs, int max_q_len, int H, int G, int window,
-                             int* status, cudaStream_t stream) {
+                             float scale, int* status, cudaStream_t stream) {
   CUtensorMap mq, mk, mv;
   constexpr bool half = std::is_same<T16, __half>::value;
   int rc = ta_make_map(&mq, q, n_tokens, (long long)H * HD, TA_BM, half);
@@ -599,7 +600,7 @@ static int launch_prefill_tc(const void* q, const void* k_rows, const void* v_ro
     attr_set = true;
   }
   const dim3 grid(H, n_seqs, (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM));
-  const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
+  const float scale_log2 = 1.4426950408889634f * score_scale(scale, HD);
   launch_pdl(attn_prefill_tc_kernel<HD, T16>, grid, dim3(TA_THREADS), smem, stream, mq, mk, mv, ca, q_start,
              (T16*)out, H, G, window, scale_log2, status);
   YALM_LAUNCH_CHECK();
@@ -609,7 +610,7 @@ static int launch_prefill_tc(const void* q, const void* k_rows, const void* v_ro
 static int ta_dispatch(const void* q, const void* k_rows, const void* v_rows, long long kv_n_rows,
                        long long kv_cols, const ta_cache_args& ca, const int* q_start, void* out, int dtype,
                        int n_tokens, int n_seqs, int max_q_len, int H, int G, int hd, int window,
-                       int* status, cudaStream_t stream) {
+                       float scale, int* status, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || n_tokens <= 0) return 0;
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (hd != 64 && hd != 128) return -2;
@@ -618,7 +619,7 @@ static int ta_dispatch(const void* q, const void* k_rows, const void* v_rows, lo
   if (((uintptr_t)q | (uintptr_t)k_rows | (uintptr_t)v_rows | (uintptr_t)out) & 15) return -6;
 #define YALM_TA(HD, T) \
   return launch_prefill_tc<HD, T>(q, k_rows, v_rows, kv_n_rows, kv_cols, ca, q_start, out, n_tokens, \
-                                  n_seqs, max_q_len, H, G, window, status, stream)
+                                  n_seqs, max_q_len, H, G, window, scale, status, stream)
   if (dtype == DT_F16) {
     if (hd == 64) YALM_TA(64, __half);
     YALM_TA(128, __half);
@@ -639,10 +640,10 @@ using namespace yalm;
 extern "C" int yalm_attention_prefill_tc(const void* q, const void* kv_step, const int* q_start,
                                          void* out, int dtype, int n_tokens, int n_seqs,
                                          int max_q_len, int H, int G, int hd, int window,
-                                         int* status, cudaStream_t stream) {
+                                         float scale, int* status, cudaStream_t stream) {
   const ta_cache_args ca = {nullptr, nullptr, nullptr, 0, 0, 0, 0};
   return ta_dispatch(q, kv_step, kv_step, n_tokens, (long long)2 * G * hd, ca, q_start, out, dtype, n_tokens,
-                     n_seqs, max_q_len, H, G, hd, window, status, stream);
+                     n_seqs, max_q_len, H, G, hd, window, scale, status, stream);
 }
 
 // The same for sequences that go on from the positions in slot_pos (prompts cut into steps):
@@ -655,7 +656,8 @@ extern "C" int yalm_attention_prefill_tc_cache(const void* q, const void* k_cach
                                                const int* q_start, const int* seq_slot,
                                                const int* slot_pos, void* out, int dtype, int n_tokens,
                                                int n_seqs, int max_q_len, int n_slots, int H, int G,
-                                               int hd, int capacity, int window, const int* page_table,
+                                               int hd, int capacity, int window, float scale,
+                                               const int* page_table,
                                                int pages_per_slot, int n_pages, int* status,
                                                cudaStream_t stream) {
   if (capacity <= 0 || n_slots <= 0 || (page_table != nullptr && (pages_per_slot <= 0 || n_pages <= 0)))
@@ -665,5 +667,5 @@ extern "C" int yalm_attention_prefill_tc_cache(const void* q, const void* k_cach
                                                : (long long)n_slots * G * capacity;
   if (rows > 0x7fffffffLL) return -4;
   return ta_dispatch(q, k_cache, v_cache, rows, hd, ca, q_start, out, dtype, n_tokens, n_seqs, max_q_len,
-                     H, G, hd, window, status, stream);
+                     H, G, hd, window, scale, status, stream);
 }

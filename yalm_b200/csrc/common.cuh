@@ -152,6 +152,27 @@ __device__ __forceinline__ float rotate_hi(float a, float b, float c, float s) {
   return __fmaf_rn(a, s, __fmul_rn(b, c));
 }
 
+// ---- which keys a query sees ------------------------------------------------
+// Besides causality (keys up to its own position) a query at position pos sees, by the
+// `window` argument of the attention kernels:  > 0: the last `window` positions;
+// < 0: the positions of its own chunk of -window positions, chunks counted from position 0
+// of the sequence;  0: every position.  The first visible position never decreases as pos
+// grows, so a tile of queries sees one run of keys from its first row's bound on.
+__host__ __device__ __forceinline__ int first_visible(int pos, int window) {
+  if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (window < 0) return pos - pos % (-window);
+  return 0;
+}
+// The most keys any query sees when no sequence is longer than max_context.
+__host__ __device__ __forceinline__ int most_visible(int max_context, int window) {
+  const int w = window < 0 ? -window : window;
+  return w > 0 && w < max_context ? w : max_context;
+}
+// log2(e) * scale, with 1 / sqrt(head size) where no scale is given (scale <= 0)
+__host__ __forceinline__ float score_scale(float scale, int hd) {
+  return scale > 0.f ? scale : 1.0f / sqrtf((float)hd);
+}
+
 // ---- where a cached row lives --------------------------------------------
 // The cache of one layer run is either contiguous per sequence,
 // [slots][kv heads][capacity][head size], or made of pages of KV_PAGE positions,

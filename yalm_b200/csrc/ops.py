@@ -58,18 +58,18 @@ _SIGNATURES = {
     "yalm_advance": [_vp, _vp, _vp, _i, _vp],
     "yalm_cache_write": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                       _i, _i, _i, _vp, _i, _i, _vp],
+                       _i, _i, _f, _i, _vp, _i, _i, _vp],
     "yalm_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                              _i, _i, _i, _i, _vp, _i, _i, _vp],
+                              _i, _i, _f, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_prefill_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                   _i, _i, _vp, _i, _i, _vp],
-    "yalm_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+                                   _i, _i, _f, _vp, _i, _i, _vp],
+    "yalm_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
     "yalm_attention_prefill_tc_cache": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
-                                        _i, _vp, _i, _i, _vp, _vp],
+                                        _i, _f, _vp, _i, _i, _vp, _vp],
     "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
-                                  _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
+                                  _i, _i, _i, _f, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_decode_mma_fused": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i,
-                                        _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
+                                        _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -78,6 +78,17 @@ _SIGNATURES = {
     "yalm_gemm_2sm_token_tile": [_i, _i, _i],
     "yalm_gemm_2sm_rope": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "yalm_rope_table": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+    "yalm_embed_pair": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll,
+                        _vp, _vp],
+    "yalm_head_gate": [_vp, _i, _vp, _i, _ll, _i, _i, _i, _vp],
+    "yalm_softcap": [_vp, _ll, _f, _vp],
+    "yalm_residual_add": [_vp, _vp, _vp, _i, _ll, _ll, _vp],
+    "yalm_route_topk": [_vp, _i, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "yalm_route_plan": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "yalm_gather_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "yalm_gemm_grouped": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "yalm_glu_clamp": [_vp, _i, _ll, _vp, _i, _ll, _i, _f, _f, _f, _vp],
+    "yalm_routed_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
 }
 
 _lib = None
@@ -137,6 +148,20 @@ def _need(cond: bool, msg: str) -> None:
 
 
 KV_PAGE = 64     # positions per page of a paged cache
+
+
+def mask_code(window: Optional[int], chunk: Optional[int] = None) -> int:
+    """The kernels' ``window`` argument: a sliding window of ``window`` positions as a positive
+    number, a chunked mask (a query sees the keys of its own chunk of ``chunk`` positions,
+    chunks counted from position 0) as the negative chunk size, 0 for neither."""
+    _need(not (window and chunk), "attention: a sliding window and a chunked mask exclude each other")
+    return -int(chunk) if chunk else int(window or 0)
+
+
+def most_visible(max_context: int, window: Optional[int], chunk: Optional[int] = None) -> int:
+    """The most keys a query sees when no sequence is longer than ``max_context``."""
+    w = int(window or chunk or 0)
+    return min(max_context, w) if w else max_context
 
 
 def _pages(pages, cache: torch.Tensor, G: int, hd: int):
@@ -256,7 +281,7 @@ def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_c
               batch, slot_pos: torch.Tensor, out: torch.Tensor, H: int, G: int, hd: int,
               capacity: int, window: Optional[int], nsplit: int = 1,
               part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-              pages=None) -> None:
+              pages=None, chunk: Optional[int] = None, scale: Optional[float] = None) -> None:
     n = q.shape[0]
     pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype,
@@ -271,7 +296,8 @@ def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_c
     _check(lib().yalm_attention(_p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.token_seq),
                                 _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos), _p(out),
                                 _p(part_o), _p(part_ml), dtype_code(q.dtype), n, H, G, hd,
-                                capacity, int(window or 0), nsplit, pt, pps, npg, _stream()), "attention",
+                                capacity, mask_code(window, chunk), float(scale or 0.0), nsplit, pt, pps, npg,
+                                _stream()), "attention",
            kernels=2 if nsplit > 1 else 1)
 
 
@@ -279,12 +305,14 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      seq_slot: torch.Tensor, slot_pos: torch.Tensor, out: torch.Tensor,
                      part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
                      status: torch.Tensor, H: int, G: int, hd: int, capacity: int,
-                     window: Optional[int], chunk: int, max_context: int, pages=None) -> None:
-    """One query per sequence over the cache (the query's own row included)."""
+                     window: Optional[int], chunk: int, max_context: int, pages=None,
+                     mask_chunk: Optional[int] = None, scale: Optional[float] = None) -> None:
+    """One query per sequence over the cache (the query's own row included).  ``chunk`` is the
+    kernel's keys per block; ``mask_chunk`` the chunk size of a chunked mask."""
     n = q.shape[0]
     pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype, "attention_decode: dtypes")
-    visible = min(max_context, window) if window else max_context
+    visible = most_visible(max_context, window, mask_chunk)
     max_chunks = -(-visible // chunk)
     hc = -(-(H // G) // 4)
     _need(part_o.numel() >= n * H * max_chunks * hd and part_ml.numel() >= n * H * max_chunks * 2
@@ -293,7 +321,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _check(lib().yalm_attention_decode(_p(q), _p(k_cache), _p(v_cache), _p(seq_slot), _p(slot_pos),
                                        _p(out), _p(part_o), _p(part_ml), _p(counters), _p(status),
                                        dtype_code(q.dtype), n, H, G, hd, capacity,
-                                       int(window or 0), chunk, max_context, pt, pps, npg, _stream()),
+                                       mask_code(window, mask_chunk), float(scale or 0.0), chunk,
+                                       max_context, pt, pps, npg, _stream()),
            "attention_decode")
 
 
@@ -306,7 +335,8 @@ def mma_attention_usable(dtype: torch.dtype, hd: int) -> bool:
 def attention_prefill_mma(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
                           v_cache: torch.Tensor, batch, slot_pos: torch.Tensor, out: torch.Tensor,
                           H: int, G: int, hd: int, capacity: int, window: Optional[int],
-                          pages=None) -> None:
+                          pages=None, chunk: Optional[int] = None,
+                          scale: Optional[float] = None) -> None:
     pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype
           and q.dtype in HALF_TYPES, "attention_prefill_mma: one 16-bit type throughout")
@@ -314,7 +344,8 @@ def attention_prefill_mma(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch
                                             _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos),
                                             _p(out), dtype_code(q.dtype), batch.n_seqs,
                                             max(batch.q_lens), H, G, hd,
-                                            capacity, int(window or 0), pt, pps, npg, _stream()),
+                                            capacity, mask_code(window, chunk), float(scale or 0.0),
+                                            pt, pps, npg, _stream()),
            "attention_prefill_mma")
 
 
@@ -332,20 +363,23 @@ def tc_attention_usable(dtype: torch.dtype, hd: int, past, q_lens=None, capacity
 
 def attention_prefill_tc(q: torch.Tensor, kv_step: torch.Tensor, batch, out: torch.Tensor,
                          H: int, G: int, hd: int, window: Optional[int],
-                         status: torch.Tensor) -> None:
+                         status: torch.Tensor, chunk: Optional[int] = None,
+                         scale: Optional[float] = None) -> None:
     _need(q.dtype == kv_step.dtype == out.dtype and q.dtype in HALF_TYPES and q.is_contiguous()
           and kv_step.is_contiguous() and out.is_contiguous(),
           "attention_prefill_tc: one 16-bit type throughout")
     _check(lib().yalm_attention_prefill_tc(_p(q), _p(kv_step), _p(batch.q_start), _p(out),
                                            dtype_code(q.dtype), q.shape[0], batch.n_seqs, max(batch.q_lens), H, G, hd,
-                                           int(window or 0), _p(status), _stream()),
+                                           mask_code(window, chunk), float(scale or 0.0), _p(status),
+                                           _stream()),
            "attention_prefill_tc")
 
 
 def attention_prefill_tc_cache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch,
                                slot_pos: torch.Tensor, out: torch.Tensor, H: int, G: int, hd: int,
                                capacity: int, window: Optional[int], status: torch.Tensor,
-                               pages=None) -> None:
+                               pages=None, chunk: Optional[int] = None,
+                               scale: Optional[float] = None) -> None:
     """attention_prefill_tc with every key (this step's too) read from the cache, which the
     step wrote before this call; for sequences that go on and do not wrap in this step."""
     pt, pps, npg = _pages(pages, k_cache, G, hd)
@@ -360,13 +394,15 @@ def attention_prefill_tc_cache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: 
                                                  _p(batch.seq_slot), _p(slot_pos), _p(out),
                                                  dtype_code(q.dtype), q.shape[0], batch.n_seqs,
                                                  max(batch.q_lens), n_slots, H, G, hd, capacity,
-                                                 int(window or 0), pt, pps, npg, _p(status), _stream()),
+                                                 mask_code(window, chunk), float(scale or 0.0), pt, pps,
+                                                 npg, _p(status), _stream()),
            "attention_prefill_tc_cache")
 
 
-def decode_mma_parts(max_context: int, window: Optional[int], chunks_per_block: int) -> int:
+def decode_mma_parts(max_context: int, window: Optional[int], chunks_per_block: int,
+                     mask_chunk: Optional[int] = None) -> int:
     """Blocks (partial results) per query of attention_decode_mma."""
-    visible = min(max_context, window) if window else max_context
+    visible = most_visible(max_context, window, mask_chunk)
     return -(-(-(-visible // 64)) // chunks_per_block)
 
 
@@ -375,13 +411,14 @@ def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
                          status: torch.Tensor, H: int, G: int, hd: int, capacity: int,
                          window: Optional[int], max_context: int, chunks_per_block: int,
-                         pages=None, warps: int = 4) -> None:
+                         pages=None, warps: int = 4, mask_chunk: Optional[int] = None,
+                         scale: Optional[float] = None) -> None:
     """``warps``: 4 (one block to an SM) or 2 (two blocks of two warps to an SM)."""
     n = q.shape[0]
     pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype and q.dtype in HALF_TYPES,
           "attention_decode_mma: one 16-bit type throughout")
-    parts = decode_mma_parts(max_context, window, chunks_per_block)
+    parts = decode_mma_parts(max_context, window, chunks_per_block, mask_chunk)
     hc = -(-(H // G) // 16)
     _need(part_o.numel() >= n * H * parts * hd and part_ml.numel() >= n * H * parts * 2
           and counters.numel() >= n * G * hc and counters.dtype == torch.int32,
@@ -389,7 +426,8 @@ def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     _check(lib().yalm_attention_decode_mma(_p(q), _p(k_cache), _p(v_cache), _p(seq_slot),
                                            _p(slot_pos), _p(out), _p(part_o), _p(part_ml),
                                            _p(counters), _p(status), dtype_code(q.dtype), n, H, G,
-                                           hd, capacity, int(window or 0), max_context,
+                                           hd, capacity, mask_code(window, mask_chunk),
+                                           float(scale or 0.0), max_context,
                                            chunks_per_block, warps, pt, pps, npg,
                                            _stream()),
            "attention_decode_mma")
@@ -400,7 +438,9 @@ def attention_decode_mma_fused(qkv: torch.Tensor, n_partials: int, cos_sin: torc
                                slot_pos: torch.Tensor, out: torch.Tensor, part_o: torch.Tensor,
                                part_ml: torch.Tensor, counters: torch.Tensor, status: torch.Tensor,
                                H: int, G: int, hd: int, capacity: int, window: Optional[int],
-                               max_context: int, chunks_per_block: int, pages=None) -> None:
+                               max_context: int, chunks_per_block: int, pages=None,
+                               mask_chunk: Optional[int] = None,
+                               scale: Optional[float] = None) -> None:
     """attention_decode_mma with the rotary kernel's work inside: ``qkv`` is this step's q/k/v
     product as float32 slices [n_partials, n, (H + 2 G) hd] (or [n, ...] for one), ``cos_sin`` the
     step's table of ``rope_table`` [n, hd / 2, 2]; q is rotated in the kernel and the new k and v
@@ -414,7 +454,7 @@ def attention_decode_mma_fused(qkv: torch.Tensor, n_partials: int, cos_sin: torc
           and tuple(cos_sin.shape) == (n, hd // 2, 2), "attention_decode_mma_fused: cos_sin [n, hd/2, 2]")
     _need(k_cache.dtype == v_cache.dtype == out.dtype and out.dtype in HALF_TYPES,
           "attention_decode_mma_fused: one 16-bit type throughout")
-    parts = decode_mma_parts(max_context, window, chunks_per_block)
+    parts = decode_mma_parts(max_context, window, chunks_per_block, mask_chunk)
     hc = -(-(H // G) // 16)
     _need(part_o.numel() >= n * H * parts * hd and part_ml.numel() >= n * H * parts * 2
           and counters.numel() >= n * G * hc and counters.dtype == torch.int32,
@@ -423,8 +463,8 @@ def attention_decode_mma_fused(qkv: torch.Tensor, n_partials: int, cos_sin: torc
                                                  _p(v_cache), _p(seq_slot), _p(slot_pos), _p(out),
                                                  _p(part_o), _p(part_ml), _p(counters), _p(status),
                                                  dtype_code(out.dtype), n, H, G, hd, capacity,
-                                                 int(window or 0), max_context, chunks_per_block, pt, pps,
-                                                 npg, _stream()),
+                                                 mask_code(window, mask_chunk), float(scale or 0.0),
+                                                 max_context, chunks_per_block, pt, pps, npg, _stream()),
            "attention_decode_mma_fused")
 
 
@@ -535,6 +575,132 @@ def gemm_2sm_rope(a: torch.Tensor, w: torch.Tensor, cos_sin: torch.Tensor, batch
     r.H, r.G, r.hd, r.capacity, r.write_cache = H, G, hd, capacity, 1 if write_cache else 0
     _check(lib().yalm_gemm_2sm_rope(_p(a), _p(w), dtype_code(a.dtype), M, N, K, ctypes.byref(r),
                                     _p(status), _stream()), "gemm_2sm_rope")
+
+
+# ---- small row-wise kernels some architectures add ------------------------------------
+def embed_pair(batch, table: torch.Tensor, pair_table: torch.Tensor, prev_token: torch.Tensor,
+               slot_pos: torch.Tensor, x: torch.Tensor, x_copy: Optional[torch.Tensor],
+               mul_prev: int, mul_cur: int, status: torch.Tensor) -> None:
+    """x[t] = table[token] + pair_table[row]; row = buckets (the table's last row) at a
+    sequence's position 0, else (previous token * mul_prev + token * mul_cur) mod buckets.
+    ``prev_token`` int32 [slots]: each sequence's last token so far, kept up to date here."""
+    n, dim = x.shape
+    _need(table.dtype == pair_table.dtype and table.shape[1] == dim == pair_table.shape[1]
+          and table.is_contiguous() and pair_table.is_contiguous() and x.dtype == torch.float32
+          and x.is_contiguous() and pair_table.shape[0] >= 2, "embed_pair: tables and x")
+    _need(prev_token.dtype == torch.int32 and prev_token.is_contiguous(), "embed_pair: prev_token int32")
+    _need(x_copy is None or (x_copy.dtype == torch.float32 and x_copy.is_contiguous()
+                             and x_copy.shape == x.shape), "embed_pair: x_copy like x")
+    _check(lib().yalm_embed_pair(_p(batch.tokens), _p(batch.token_seq), _p(batch.q_start),
+                                 _p(batch.seq_slot), _p(slot_pos), _p(table), _p(pair_table),
+                                 dtype_code(table.dtype), _p(prev_token), _p(x), _p(x_copy), n, dim,
+                                 table.shape[0], pair_table.shape[0] - 1, int(mul_prev), int(mul_cur),
+                                 _p(status), _stream()), "embed_pair")
+
+
+def head_gate(o: torch.Tensor, g: torch.Tensor, n_partials: int, H: int, hd: int) -> None:
+    """o [n, H * hd] *= sigmoid(g) per head; g float32 [n_partials, n, H] slices that are summed."""
+    n = o.shape[0]
+    _need(o.is_contiguous() and o.shape[1] == H * hd and g.dtype == torch.float32 and g.is_contiguous()
+          and g.numel() >= n_partials * n * H, "head_gate: shapes")
+    _check(lib().yalm_head_gate(_p(o), dtype_code(o.dtype), _p(g), n_partials, n * H, n, H, hd, _stream()),
+           "head_gate")
+
+
+def softcap(v: torch.Tensor, cap: float) -> None:
+    """v <- cap * tanh(v / cap), in place, float32."""
+    _need(v.dtype == torch.float32 and v.is_contiguous(), "softcap: float32")
+    _check(lib().yalm_softcap(_p(v), v.numel(), float(cap), _stream()), "softcap")
+
+
+def residual_add(x: torch.Tensor, y: torch.Tensor, partials: Optional[torch.Tensor] = None,
+                 n_partials: int = 0) -> None:
+    """x += y (+ the sum of ``n_partials`` slices shaped like x), float32."""
+    _need(x.dtype == y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
+          and x.numel() == y.numel(), "residual_add: float32 tensors of one size")
+    if n_partials:
+        _need(partials is not None and partials.dtype == torch.float32 and partials.is_contiguous()
+              and partials.numel() >= n_partials * x.numel(), "residual_add: partials")
+    _check(lib().yalm_residual_add(_p(x), _p(y), _p(partials) if n_partials else None, n_partials,
+                                   x.numel(), x.numel(), _stream()), "residual_add")
+
+
+# ---- a routed feed-forward --------------------------------------------------------------
+ROUTED_TILE = 64          # rows per tile of the grouped FMA product
+
+
+def route_topk(z: torch.Tensor, n_partials: int, n_tokens: int, E: int, n_groups: int, keep: int,
+               top: int, renormalise: bool, choice: torch.Tensor, weight: torch.Tensor,
+               counts: torch.Tensor) -> None:
+    """Router logits z (float32 slices [n_partials, n_tokens, E]) -> the ``top`` experts of each
+    token among the ``keep`` best of ``n_groups`` groups and their softmax scores."""
+    _need(z.dtype == torch.float32 and z.is_contiguous() and z.numel() >= n_partials * n_tokens * E,
+          "route_topk: logits")
+    _need(choice.dtype == torch.int32 and weight.dtype == torch.float32 and counts.dtype == torch.int32
+          and choice.numel() >= n_tokens * top and weight.numel() >= n_tokens * top
+          and counts.numel() >= E, "route_topk: outputs")
+    _check(lib().yalm_route_topk(_p(z), n_partials, n_tokens * E, n_tokens, E, n_groups, keep, top,
+                                 1 if renormalise else 0, _p(choice), _p(weight), _p(counts), _stream()),
+           "route_topk")
+
+
+def routed_max_tiles(n_pairs: int, E: int, tile_rows: int = ROUTED_TILE) -> int:
+    return -(-n_pairs // tile_rows) + E
+
+
+def route_plan(counts, choice, n_pairs: int, top: int, E: int, first_row, pair_row, row_token,
+               tile_expert, tile_row0, n_tiles, tile_rows: int = ROUTED_TILE) -> None:
+    for t in (counts, choice, first_row, pair_row, row_token, tile_expert, tile_row0, n_tiles):
+        _need(t.dtype == torch.int32 and t.is_contiguous(), "route_plan: int32 tensors")
+    _need(first_row.numel() >= E + 1 and pair_row.numel() >= n_pairs and row_token.numel() >= n_pairs
+          and tile_expert.numel() >= routed_max_tiles(n_pairs, E, tile_rows)
+          and tile_row0.numel() >= routed_max_tiles(n_pairs, E, tile_rows), "route_plan: sizes")
+    _check(lib().yalm_route_plan(_p(counts), _p(choice), n_pairs, top, E, tile_rows, _p(first_row),
+                                 _p(pair_row), _p(row_token), _p(tile_expert), _p(tile_row0),
+                                 _p(n_tiles), _stream()), "route_plan")
+
+
+def gather_rows(src: torch.Tensor, row_token: torch.Tensor, dst: torch.Tensor) -> None:
+    rows, dim = dst.shape
+    _need(src.dtype == dst.dtype and src.shape[1] == dim and src.is_contiguous() and dst.is_contiguous()
+          and row_token.dtype == torch.int32 and row_token.numel() >= rows, "gather_rows: shapes")
+    _check(lib().yalm_gather_rows(_p(src), _p(row_token), _p(dst), dtype_code(dst.dtype), rows, dim,
+                                  _stream()), "gather_rows")
+
+
+def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, first_row, tile_expert,
+                 tile_row0, n_tiles, max_tiles: int) -> None:
+    """out[r] = a[r] @ w[e].T for the rows of every expert e (a in sorted order, w [E, N, K]),
+    with 32-bit FMA; the plan's tiles must be ROUTED_TILE rows."""
+    rows, K = a.shape
+    E, N, _ = w.shape
+    _need(w.shape[2] == K and tuple(out.shape) == (rows, N) and a.is_contiguous() and w.is_contiguous()
+          and out.is_contiguous(), "gemm_grouped: shapes")
+    _check(lib().yalm_gemm_grouped(_p(a), dtype_code(a.dtype), _p(w), dtype_code(w.dtype), _p(out),
+                                   dtype_code(out.dtype), _p(first_row), _p(tile_expert),
+                                   _p(tile_row0), _p(n_tiles), max_tiles, N, K, _stream()),
+           "gemm_grouped")
+
+
+def glu_clamp(gu: torch.Tensor, out: torch.Tensor, n_partials: int, alpha: float, limit: float,
+              shift: float) -> None:
+    """out = g' * sigmoid(alpha g') * (u' + shift), g' = min(g, limit), u' = clamp(u, +-limit)
+    (no clamps when limit <= 0); gu float32 [(n_partials,) rows, 2F] as (gate | up)."""
+    rows, F = out.shape
+    _need(gu.dtype == torch.float32 and gu.shape[-1] == 2 * F and gu.shape[-2] == rows
+          and gu.is_contiguous() and out.is_contiguous(), "glu_clamp: shapes")
+    _check(lib().yalm_glu_clamp(_p(gu), n_partials, rows * 2 * F, _p(out), dtype_code(out.dtype), rows, F,
+                                float(alpha), float(limit), float(shift), _stream()), "glu_clamp")
+
+
+def routed_combine(x: torch.Tensor, y: torch.Tensor, pair_row: torch.Tensor, weight: torch.Tensor,
+                   top: int) -> None:
+    """x[t] += sum_j weight[t, j] * y[pair_row[t, j]]."""
+    n, dim = x.shape
+    _need(x.dtype == y.dtype == weight.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
+          and y.shape[1] == dim and pair_row.dtype == torch.int32, "routed_combine: shapes")
+    _check(lib().yalm_routed_combine(_p(x), _p(y), _p(pair_row), _p(weight), n, top, dim, _stream()),
+           "routed_combine")
 
 
 def sample(logits: torch.Tensor, temperature: float, seed: int, row_key: torch.Tensor,

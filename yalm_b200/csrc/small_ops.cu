@@ -1,0 +1,166 @@
+// Small row-wise kernels that some architectures add around the common ones:
+//  * an embedding with a second, hashed table: x = E[token] + P[row], where row is a hash of
+//    the previous and the current token (the previous token of a sequence's first token in a
+//    step comes from a per-sequence state that the kernel also updates);
+//  * a per-head output gate: o[t, h, :] *= sigmoid(g[t, h]);
+//  * a soft cap on logits: v <- cap * tanh(v / cap);
+//  * x += y on the residual stream, folding pending split-K partial sums in.
+// All arithmetic is 32-bit.
+#include "api.h"
+#include "common.cuh"
+
+namespace yalm {
+
+template <typename T>
+__global__ void embed_pair_kernel(const int* __restrict__ tokens, const int* __restrict__ token_seq,
+                                  const int* __restrict__ q_start, const int* __restrict__ seq_slot,
+                                  const int* __restrict__ slot_pos, const T* __restrict__ table,
+                                  const T* __restrict__ pair_table, int* __restrict__ prev_token,
+                                  float* __restrict__ x, float* __restrict__ x_copy, int dim, int vocab,
+                                  int buckets, long long mul_prev, long long mul_cur,
+                                  int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  if (tok < 0 || tok >= vocab) {
+    if (threadIdx.x == 0) atomicOr(status, ERR_TOKEN_RANGE);
+    tok = tok < 0 ? 0 : vocab - 1;
+  }
+  const int b = token_seq[t];
+  const int slot = seq_slot[b];
+  const int qs = q_start[b];
+  const int pos = slot_pos[slot] + (t - qs);
+  // the token before this one: the step's own, or what the sequence's last step left
+  int prev = t > qs ? tokens[t - 1] : prev_token[slot];
+  prev = prev < 0 ? 0 : (prev >= vocab ? vocab - 1 : prev);
+  long long row = buckets;                                   // a sequence's first token: the last row
+  if (pos > 0) {
+    row = ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
+    if (row < 0) row += buckets;
+  }
+  const T* e = table + (size_t)tok * dim;
+  const T* p = pair_table + (size_t)row * dim;
+  float* out = x + (size_t)t * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = to_float(e[i]) + to_float(p[i]);
+    out[i] = v;
+    if (x_copy != nullptr) x_copy[(size_t)t * dim + i] = v;
+  }
+  // Only the block of a sequence's first token in this step reads the state, and it alone
+  // writes it, after every one of its threads has read: the step's last token.
+  if (t == qs) {
+    __syncthreads();
+    if (threadIdx.x == 0) prev_token[slot] = tokens[q_start[b + 1] - 1];
+  }
+}
+
+// o [n, H, hd] *= sigmoid(sum over slices of g [S, n, H]); one block per token
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ o, const float* __restrict__ g, int n_partials,
+                                 long long partial_stride, int H, int hd) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float gate_s[];
+  const int t = blockIdx.x;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float z = 0.f;
+    for (int s = 0; s < n_partials; ++s) z += g[(size_t)s * partial_stride + (size_t)t * H + h];
+    gate_s[h] = 1.0f / (1.0f + expf(-z));
+  }
+  __syncthreads();
+  T* row = o + (size_t)t * H * hd;
+  for (int i = threadIdx.x; i < H * hd; i += blockDim.x)
+    row[i] = from_float<T>(to_float(row[i]) * gate_s[i / hd]);
+}
+
+__global__ void softcap_kernel(float* __restrict__ v, long long n, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) v[i] = cap * tanhf(v[i] / cap);
+}
+
+__global__ void residual_add_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                    const float* __restrict__ partials, int n_partials,
+                                    long long partial_stride, long long n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = x[i];
+  for (int s = 0; s < n_partials; ++s) v += partials[(size_t)s * partial_stride + i];
+  x[i] = v + y[i];
+}
+
+}  // namespace yalm
+
+using namespace yalm;
+
+// x[t] = E[token t] + P[row t] (and the same into x_copy when it is given).  row = buckets
+// for position 0 of a sequence, else (previous token * mul_prev + token * mul_cur) mod
+// buckets; pair_table has buckets + 1 rows.  prev_token [slots]: the last token each sequence
+// has been given so far (read for a step's first token, then set to the step's last).
+extern "C" int yalm_embed_pair(const int* tokens, const int* token_seq, const int* q_start,
+                               const int* seq_slot, const int* slot_pos, const void* table,
+                               const void* pair_table, int table_dtype, int* prev_token, float* x,
+                               float* x_copy, int n_tokens, int dim, int vocab, int buckets,
+                               long long mul_prev, long long mul_cur, int* status,
+                               cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (buckets <= 0 || dim <= 0) return -2;
+  const dim3 grid(n_tokens), block(dim >= 1024 ? 256 : 128);
+#define YALM_EP(T)                                                                                  \
+  launch_pdl(embed_pair_kernel<T>, grid, block, 0, stream, tokens, token_seq, q_start, seq_slot,   \
+             slot_pos, (const T*)table, (const T*)pair_table, prev_token, x, x_copy, dim, vocab,    \
+             buckets, mul_prev, mul_cur, status)
+  if (table_dtype == DT_F32) YALM_EP(float);
+  else if (table_dtype == DT_BF16) YALM_EP(__nv_bfloat16);
+  else if (table_dtype == DT_F16) YALM_EP(__half);
+  else return -3;
+#undef YALM_EP
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int yalm_head_gate(void* o, int dtype, const float* g, int n_partials,
+                              long long partial_stride, int n_tokens, int H, int hd,
+                              cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || hd <= 0 || H > 12000) return -2;
+  const dim3 grid(n_tokens), block(256);
+  const size_t smem = (size_t)H * sizeof(float);
+  if (dtype == DT_F32)
+    launch_pdl(head_gate_kernel<float>, grid, block, smem, stream, (float*)o, g, n_partials, partial_stride, H, hd);
+  else if (dtype == DT_BF16)
+    launch_pdl(head_gate_kernel<__nv_bfloat16>, grid, block, smem, stream, (__nv_bfloat16*)o, g, n_partials,
+               partial_stride, H, hd);
+  else if (dtype == DT_F16)
+    launch_pdl(head_gate_kernel<__half>, grid, block, smem, stream, (__half*)o, g, n_partials, partial_stride, H, hd);
+  else
+    return -3;
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int yalm_softcap(float* v, long long n, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!(cap > 0.f)) return -2;
+  const long long blocks = (n + 255) / 256;
+  if (blocks > 0x7fffffffLL) return -4;
+  launch_pdl(softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, v, n, cap);
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+// x += y (+ the sum of n_partials slices [n_partials][n]); all float32 of n elements
+extern "C" int yalm_residual_add(float* x, const float* y, const float* partials, int n_partials,
+                                 long long partial_stride, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const long long blocks = (n + 255) / 256;
+  if (blocks > 0x7fffffffLL) return -4;
+  launch_pdl(residual_add_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, y, partials, n_partials,
+             partial_stride, n);
+  YALM_LAUNCH_CHECK();
+  return 0;
+}

@@ -61,8 +61,8 @@ class LM:
         self.model = Model(self.spec, self.rt)
         ignorable = getattr(config, "ignorable_tensor", None)
         self.model.bind(tensors, ignore_unexpected=[n for n in tensors if ignorable(n)] if ignorable else ())
-        context = self.spec.max_positions if not max_context else min(int(max_context),
-                                                                     self.spec.max_positions)
+        own = self.spec.default_context or self.spec.max_positions
+        context = own if not max_context else min(int(max_context), self.spec.max_positions)
         self.engine = Engine(self.model, max_batch, context, max_tokens)
         self._next_key = 0
 

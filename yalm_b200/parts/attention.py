@@ -1,4 +1,4 @@
-"""Grouped-query causal attention with an optional sliding window.
+"""Grouped-query causal attention with an optional sliding window or chunked mask.
 
 q = Wq h, k = Wk h, v = Wv h (one product over the stacked matrix); position
 encoding on q and k; k, v into the cache; softmax((q.k)/sqrt(hd)) v over the
@@ -6,6 +6,19 @@ visible keys with head h reading kv head h // (H/G); x += Wo o.  The formulas
 are the reference's (infer.cpp:278-338, infer.cu:730-920); the window
 (keys p-W+1..p) is the checkpoint's ``sliding_window``, which the reference
 does not read.
+
+Options beyond that, each a parameter (all off for the Llama / Mistral decoder):
+
+* ``scale``: the factor on q.k in place of 1/sqrt(hd);
+* ``chunk``: a query at position p sees the keys j <= p of its own chunk,
+  p // chunk == j // chunk, chunks counted from position 0 of the sequence.  Keys of
+  earlier chunks are never read again, so the cache keeps a ring of ``chunk`` rows per
+  sequence (position p at row p % chunk), as it keeps ``window`` rows under a window;
+* ``value_dim``: a value size that differs from the query/key size.  The kernels take one
+  head size, so the smaller of the two is padded with zero rows of the weights (zero
+  columns of Wo): scores and outputs are unchanged, and nothing is padded when they agree.
+  Only an encoding without rotation allows it (rotation pairs depend on the head size);
+* ``head_gate``: head h's output is multiplied by sigmoid(Wg h)_h, Wg [H, width], before Wo.
 """
 from __future__ import annotations
 
@@ -28,32 +41,70 @@ class GQAAttention:
         self.D = int(params["hidden_size"])
         self.H = int(params["num_heads"])
         self.G = int(params["num_kv_heads"])
-        self.hd = int(params["head_dim"])
-        self.window: Optional[int] = params.get("window")
+        self.hd_k = int(params["head_dim"])
+        self.hd_v = int(params.get("value_dim") or self.hd_k)
+        self.window: Optional[int] = params.get("window") or None
+        self.chunk: Optional[int] = params.get("chunk") or None
+        self.scale: Optional[float] = params.get("scale") or None
+        self.head_gate = bool(params.get("head_gate", False))
+        if self.window and self.chunk:
+            raise ValueError("a sliding window and a chunked mask exclude each other")
         if self.H % self.G:
             raise ValueError(f"{self.H} heads do not divide into {self.G} kv heads")
-        if self.hd % 8 or not 0 < self.hd <= 256:
+        position = params["position"]
+        # the one head size the kernels run with
+        self.hd = max(self.hd_k, self.hd_v)
+        if self.hd_k != self.hd_v or self.hd % 8:
+            if position.kind != "none":
+                raise ValueError(f"head sizes {self.hd_k} (keys) and {self.hd_v} (values) need padding "
+                                 f"to one multiple of 8, which a rotating position encoding rules out")
+            self.hd = -(-self.hd // 16) * 16
+            position = type(position)(position.kind, {**position.params, "head_dim": self.hd},
+                                      position.tensors)
+        if not 0 < self.hd <= 256:
             raise ValueError(f"head size {self.hd} is not supported by the attention kernel "
-                             f"(multiples of 8 up to 256)")
-        self.position = make_part(POSITIONS, params["position"], rt)
+                             f"(up to 256)")
+        self.span = self.window or self.chunk          # the most keys a query sees, if bounded
+        self.position = make_part(POSITIONS, position, rt)
         self.w_qkv = None
         self.w_o = None
+        self.w_g = None
 
     def tensor_needs(self):
-        return {"q": TensorNeed((self.H * self.hd, self.D)),
-                "k": TensorNeed((self.G * self.hd, self.D)),
-                "v": TensorNeed((self.G * self.hd, self.D)),
-                "o": TensorNeed((self.D, self.H * self.hd))}
+        needs = {"q": TensorNeed((self.H * self.hd_k, self.D)),
+                 "k": TensorNeed((self.G * self.hd_k, self.D)),
+                 "v": TensorNeed((self.G * self.hd_v, self.D)),
+                 "o": TensorNeed((self.D, self.H * self.hd_v))}
+        if self.head_gate:
+            needs["g"] = TensorNeed((self.H, self.D))
+        return needs
+
+    def _pad_heads(self, w: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+        """[heads * size, D] -> [heads * hd, D] with zero rows after each head's own."""
+        if size == self.hd:
+            return w
+        out = torch.zeros((heads, self.hd, w.shape[1]), dtype=w.dtype, device=w.device)
+        out[:, :size] = w.view(heads, size, w.shape[1])
+        return out.view(heads * self.hd, w.shape[1])
 
     def bind(self, tensors) -> None:
-        parts = [tensors["q"], tensors["k"], tensors["v"]]
+        parts = [self._pad_heads(tensors["q"], self.H, self.hd_k),
+                 self._pad_heads(tensors["k"], self.G, self.hd_k),
+                 self._pad_heads(tensors["v"], self.G, self.hd_v)]
         if any(p.dtype == torch.float32 for p in parts):
             parts = [p.to(torch.float32) for p in parts]
         self.w_qkv = self.rt.matrix(torch.cat(parts, 0))
-        self.w_o = self.rt.matrix(tensors["o"])
+        w_o = tensors["o"]
+        if self.hd_v != self.hd:
+            padded = torch.zeros((self.D, self.H, self.hd), dtype=w_o.dtype, device=w_o.device)
+            padded[:, :, :self.hd_v] = w_o.view(self.D, self.H, self.hd_v)
+            w_o = padded.view(self.D, self.H * self.hd)
+        self.w_o = self.rt.matrix(w_o)
+        if self.head_gate:
+            self.w_g = self.rt.matrix(tensors["g"])
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=self.window)
+        return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=self.span)
 
     def decode_chunk(self, batch) -> int:
         """Keys per block of the decode kernel: 64 KiB of keys and values, so
@@ -70,7 +121,7 @@ class GQAAttention:
         chunk all split in two, the grid doubles and every query is merged (measured at 7B
         sizes, 16 sequences of 700 keys: 3.46 against 3.10 ms per step)."""
         slack = max(0, max(1, batch.ctx_bound) - (max(batch.past) + 1))
-        return [-(-(min(p + 1 + slack, self.window) if self.window else p + 1 + slack) // 64)
+        return [-(-(min(p + 1 + slack, self.span) if self.span else p + 1 + slack) // 64)
                 for p in batch.past]
 
     def decode_chunks_per_block(self, batch, visible: int) -> int:
@@ -118,18 +169,25 @@ class GQAAttention:
 
     def cache_read_bytes(self, contexts, element_size: int) -> int:
         """Bytes of keys and values one decode step reads for sequences of these lengths."""
-        seen = sum(min(c, self.window) if self.window else c for c in contexts)
+        if self.chunk:
+            seen = sum((c - 1) % self.chunk + 1 for c in contexts if c > 0)
+        else:
+            seen = sum(min(c, self.window) if self.window else c for c in contexts)
         return seen * 2 * self.G * self.hd * element_size
 
     def flops(self, q_lens, past) -> float:
         """Multiply-adds times two of a step: the four projections and, for each query,
         scores and value mix over the keys it sees."""
         n = sum(q_lens)
-        linear = 2.0 * n * ((self.H + 2 * self.G) * self.hd * self.D + self.D * self.H * self.hd)
+        linear = 2.0 * n * ((self.H + 2 * self.G) * self.hd * self.D + self.D * self.H * self.hd
+                            + (self.H * self.D if self.head_gate else 0))
         pairs = 0
         for q, p in zip(q_lens, past):
             for pos in range(p, p + q):
-                pairs += min(pos + 1, self.window) if self.window else pos + 1
+                if self.chunk:
+                    pairs += pos % self.chunk + 1
+                else:
+                    pairs += min(pos + 1, self.window) if self.window else pos + 1
         return linear + 4.0 * self.H * self.hd * pairs
 
     def forward(self, h, batch, stream, view, shared: bool = False):
@@ -142,6 +200,10 @@ class GQAAttention:
                  and ops.gemm_2sm_rope_usable(h, self.w_qkv, hd))
         if not fused:
             qkv, S = matmul_partials(rt, h, self.w_qkv, "qkv")
+        if self.head_gate:
+            gate, gate_S = matmul_partials(rt, h, self.w_g, "head_gate")
+        mask = {"chunk": self.chunk, "scale": self.scale}
+        dmask = {"mask_chunk": self.chunk, "scale": self.scale}
         tensor_cores = ops.mma_attention_usable(rt.dtype, hd) and rt.attention != "simt"
         # one token per sequence on the tensor-core kernel, a small batch: that kernel sums the
         # product's slices, rotates and writes the cache row itself (no rotary kernel, one
@@ -178,11 +240,11 @@ class GQAAttention:
         if batch.is_decode:
             # one query per sequence, every key already in the cache
             bound = max(1, batch.ctx_bound)
-            visible = min(bound, self.window) if self.window else bound
+            visible = min(bound, self.span) if self.span else bound
             if tensor_cores:
                 cpc = self.decode_chunks_per_block(batch, visible)
                 warps = 4 if in_attention else self.decode_warps(batch, visible, cpc)
-                parts = ops.decode_mma_parts(bound, self.window, cpc)
+                parts = ops.decode_mma_parts(bound, self.window, cpc, self.chunk)
             else:
                 chunk = self.decode_chunk(batch)
                 parts = -(-visible // chunk)
@@ -193,16 +255,16 @@ class GQAAttention:
                 ops.attention_decode_mma_fused(qkv, S, table(batch, view.slot_pos), view.k, view.v,
                                                batch.seq_slot, view.slot_pos, o, part_o, part_ml,
                                                counters, rt.status, H, G, hd, view.capacity,
-                                               self.window, bound, cpc, pages=view.pages)
+                                               self.window, bound, cpc, pages=view.pages, **dmask)
             elif tensor_cores:
                 ops.attention_decode_mma(q, view.k, view.v, batch.seq_slot, view.slot_pos, o,
                                          part_o, part_ml, counters, rt.status, H, G, hd,
                                          view.capacity, self.window, bound, cpc, pages=view.pages,
-                                         warps=warps)
+                                         warps=warps, **dmask)
             else:
                 ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
                                      part_ml, counters, rt.status, H, G, hd, view.capacity,
-                                     self.window, chunk, bound, pages=view.pages)
+                                     self.window, chunk, bound, pages=view.pages, **dmask)
         elif rt.attention in ("auto", "tcgen05") and ops.tc_attention_usable(
                 rt.dtype, hd, batch.past, batch.q_lens, view.capacity):
             # S, P and O in tensor memory, two query tiles per block in ping-pong (41 us
@@ -211,16 +273,19 @@ class GQAAttention:
             # not wrap around their ring in this step) read every key from the cache, which
             # holds this step's rows by now.
             if all(p == 0 for p in batch.past):
-                ops.attention_prefill_tc(q, kv_step, batch, o, H, G, hd, self.window, rt.status)
+                ops.attention_prefill_tc(q, kv_step, batch, o, H, G, hd, self.window, rt.status, **mask)
             else:
                 ops.attention_prefill_tc_cache(q, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
-                                               view.capacity, self.window, rt.status, pages=view.pages)
+                                               view.capacity, self.window, rt.status, pages=view.pages,
+                                               **mask)
         elif tensor_cores:
             ops.attention_prefill_mma(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G,
-                                      hd, view.capacity, self.window, pages=view.pages)
+                                      hd, view.capacity, self.window, pages=view.pages, **mask)
         else:
             ops.attention(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
-                          view.capacity, self.window, 1, None, None, pages=view.pages)
+                          view.capacity, self.window, 1, None, None, pages=view.pages, **mask)
+        if self.head_gate:
+            ops.head_gate(o, gate, gate_S, H, hd)
         stream.add_linear(o, self.w_o)
         if late_write:
             def write_ring():

@@ -217,5 +217,11 @@ class ResidualStream:
         return self.x
 
     def add_tensor(self, y: torch.Tensor) -> None:
+        """x += y, and the pending partial sums with it."""
+        if y.dtype == torch.float32 and y.is_contiguous() and y.shape == self.x.shape \
+                and self.x.is_cuda:
+            ops.residual_add(self.x, y, self.pending, self.n_pending)
+            self.pending, self.n_pending = None, 0
+            return
         self.resolve()
         self.x += y.to(torch.float32)

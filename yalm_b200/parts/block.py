@@ -19,14 +19,19 @@ class PreNormBlock:
         self.spec = layer_spec
         self.mixer_norm = make_part(NORMS, layer_spec.part("mixer_norm"), rt)
         self.mixer = make_part(MIXERS, layer_spec.part("mixer"), rt)
-        self.ffn_norm = make_part(NORMS, layer_spec.part("feed_forward_norm"), rt)
-        self.ffn = make_part(FEED_FORWARDS, layer_spec.part("feed_forward"), rt)
+        # a layer may have no feed-forward: then it is x += mixer(norm(x)) alone
+        self.ffn = self.ffn_norm = None
+        if "feed_forward" in layer_spec.parts:
+            self.ffn_norm = make_part(NORMS, layer_spec.part("feed_forward_norm"), rt)
+            self.ffn = make_part(FEED_FORWARDS, layer_spec.part("feed_forward"), rt)
 
     def parts(self):
         """(part, its PartSpec) pairs, for weight binding."""
         s = self.spec
-        return [(self.mixer_norm, s.part("mixer_norm")), (self.mixer, s.part("mixer")),
-                (self.ffn_norm, s.part("feed_forward_norm")), (self.ffn, s.part("feed_forward"))]
+        out = [(self.mixer_norm, s.part("mixer_norm")), (self.mixer, s.part("mixer"))]
+        if self.ffn is not None:
+            out += [(self.ffn_norm, s.part("feed_forward_norm")), (self.ffn, s.part("feed_forward"))]
+        return out
 
     def mixers(self):
         """name -> mixer, for the cache's needs."""
@@ -37,6 +42,7 @@ class PreNormBlock:
         once every run entry that reads this entry's cache has run."""
         h = self.mixer_norm(stream)
         later = self.mixer.forward(h, batch, stream, views["mixer"], shared=shared)
-        h = self.ffn_norm(stream)
-        self.ffn.forward(h, batch, stream)
+        if self.ffn is not None:
+            h = self.ffn_norm(stream)
+            self.ffn.forward(h, batch, stream)
         return later

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import torch
 
+from ..csrc import ops
 from ..weights import TensorNeed
 from .base import register_feed_forward
 from .linear import matmul_silu_mul
@@ -47,3 +48,137 @@ class SwiGLU:
         act = self.rt.buffer("ffn_act", (h.shape[0], self.F), self.rt.dtype)
         matmul_silu_mul(self.rt, h, self.w_gate_up, act, self.paired)
         stream.add_linear(act, self.w_down)
+
+
+class ClampedGLU:
+    """One gated feed-forward with clamps, y = down(g' sigmoid(slope g') (u' + shift)) with
+    g' = min(gate h, limit) and u' = clamp(up h, -limit, limit): the shared expert of a routed
+    feed-forward (and, with its constants, any dense feed-forward of that form).  Gate and up
+    rows are one stacked matrix; the activation sums the product's K slices as it reads them."""
+
+    def __init__(self, params: dict, rt, D: int):
+        self.rt = rt
+        self.D = D
+        self.F = int(params["intermediate_size"])
+        self.limit = float(params.get("limit") or 0.0)
+        self.slope = float(params.get("slope", 1.0))
+        self.shift = float(params.get("shift", 0.0))
+        self.w_gate_up = None
+        self.w_down = None
+
+    def tensor_needs(self, prefix: str = ""):
+        return {f"{prefix}gate": TensorNeed((self.F, self.D)), f"{prefix}up": TensorNeed((self.F, self.D)),
+                f"{prefix}down": TensorNeed((self.D, self.F))}
+
+    def bind(self, gate, up, down) -> None:
+        parts = [gate, up]
+        if any(p.dtype == torch.float32 for p in parts):
+            parts = [p.to(torch.float32) for p in parts]
+        self.w_gate_up = self.rt.matrix(torch.cat(parts, 0))
+        self.w_down = self.rt.matrix(down)
+
+    def flops(self, n_tokens: int) -> float:
+        return 2.0 * n_tokens * 3 * self.F * self.D
+
+    def forward(self, h, stream, name: str) -> None:
+        from .linear import matmul_partials
+        gu, S = matmul_partials(self.rt, h, self.w_gate_up, name + "_gate_up")
+        act = self.rt.buffer(name + "_act", (h.shape[0], self.F), self.rt.dtype)
+        ops.glu_clamp(gu, act, S, self.slope, self.limit, self.shift)
+        stream.add_linear(act, self.w_down)
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts:
+    """A mixture of experts: router logits z = Wr h and scores = softmax(z) over all experts
+    in 32 bits; the experts form ``groups`` equal groups of neighbours, a group's score is its
+    largest expert score, only experts of the ``keep_groups`` best groups are eligible, each
+    token uses the ``top`` eligible experts with the largest scores, weighted by those scores
+    (divided by their sum with ``renormalise``); x += sum_j w_j expert_j(h) + shared(h).
+
+    The step: router product -> ``route_topk`` -> ``route_plan`` (the (token, choice) pairs
+    sorted by expert, on the device: nothing comes back to the host, so a decode step with
+    experts is captured into a graph like any other) -> the tokens' rows gathered in that order
+    -> grouped gate/up product -> clamped activation -> grouped down product -> weighted sum
+    into the residual stream by token, in the order of the choices."""
+
+    def __init__(self, params: dict, rt):
+        self.rt = rt
+        self.D = int(params["hidden_size"])
+        self.F = int(params["intermediate_size"])
+        self.E = int(params["experts"])
+        self.top = int(params["top"])
+        self.groups = int(params.get("groups") or 1)
+        self.keep = int(params.get("keep_groups") or self.groups)
+        self.renormalise = bool(params.get("renormalise", False))
+        self.limit = float(params.get("limit") or 0.0)
+        self.slope = float(params.get("slope", 1.0))
+        self.shift = float(params.get("shift", 0.0))
+        if self.E % self.groups or not 0 < self.keep <= self.groups:
+            raise ValueError(f"{self.E} experts do not form {self.groups} equal groups "
+                             f"of which {self.keep} are kept")
+        if not 0 < self.top <= self.keep * (self.E // self.groups):
+            raise ValueError(f"top={self.top} exceeds the experts of the kept groups")
+        self.shared = ClampedGLU(params["shared"], rt, self.D) if params.get("shared") else None
+        self.w_router = None
+        self.w_gate_up = None          # [E, 2F, D]: gate rows, then up rows, per expert
+        self.w_down = None             # [E, D, F]
+
+    def tensor_needs(self):
+        needs = {"router": TensorNeed((self.E, self.D))}
+        for j in range(self.E):
+            needs[f"gate.{j}"] = TensorNeed((self.F, self.D))
+            needs[f"up.{j}"] = TensorNeed((self.F, self.D))
+            needs[f"down.{j}"] = TensorNeed((self.D, self.F))
+        if self.shared is not None:
+            needs.update(self.shared.tensor_needs("shared."))
+        return needs
+
+    def bind(self, tensors) -> None:
+        self.w_router = self.rt.matrix(tensors["router"])
+        names = [f"{k}.{j}" for j in range(self.E) for k in ("gate", "up", "down")]
+        wide = any(tensors[n].dtype == torch.float32 for n in names)
+        get = lambda n: tensors[n].to(torch.float32) if wide else tensors[n]
+        self.w_gate_up = self.rt.matrix(torch.stack(
+            [torch.cat([get(f"gate.{j}"), get(f"up.{j}")], 0) for j in range(self.E)], 0))
+        self.w_down = self.rt.matrix(torch.stack([get(f"down.{j}") for j in range(self.E)], 0))
+        if self.shared is not None:
+            self.shared.bind(tensors["shared.gate"], tensors["shared.up"], tensors["shared.down"])
+
+    def flops(self, q_lens, past) -> float:
+        n = sum(q_lens)
+        total = 2.0 * n * (self.E * self.D + self.top * 3 * self.F * self.D)
+        return total + (self.shared.flops(n) if self.shared is not None else 0.0)
+
+    def forward(self, h, batch, stream) -> None:
+        from .linear import matmul_partials
+        rt, E, top, D, F = self.rt, self.E, self.top, self.D, self.F
+        n = h.shape[0]
+        pairs = n * top
+        i32 = torch.int32
+        z, S = matmul_partials(rt, h, self.w_router, "router_logits")
+        choice = rt.buffer("routed_choice", (pairs,), i32)
+        weight = rt.buffer("routed_weight", (pairs,), torch.float32)
+        counts = rt.zeros("routed_counts", E)
+        ops.route_topk(z, S, n, E, self.groups, self.keep, top, self.renormalise, choice, weight, counts)
+        max_tiles = ops.routed_max_tiles(pairs, E)
+        first_row = rt.buffer("routed_first_row", (E + 1,), i32)
+        pair_row = rt.buffer("routed_pair_row", (pairs,), i32)
+        row_token = rt.buffer("routed_row_token", (pairs,), i32)
+        tile_expert = rt.buffer("routed_tile_expert", (max_tiles,), i32)
+        tile_row0 = rt.buffer("routed_tile_row0", (max_tiles,), i32)
+        n_tiles = rt.buffer("routed_n_tiles", (1,), i32)
+        ops.route_plan(counts, choice, pairs, top, E, first_row, pair_row, row_token, tile_expert,
+                       tile_row0, n_tiles)
+        plan = (first_row, tile_expert, tile_row0, n_tiles, max_tiles)
+        rows = rt.buffer("routed_rows", (pairs, D), h.dtype)
+        ops.gather_rows(h, row_token, rows)
+        gu = rt.buffer("routed_gate_up", (pairs, 2 * F), torch.float32)
+        ops.gemm_grouped(rows, self.w_gate_up, gu, *plan)
+        act = rt.buffer("routed_act", (pairs, F), rt.dtype)
+        ops.glu_clamp(gu, act, 1, self.slope, self.limit, self.shift)
+        y = rt.buffer("routed_out", (pairs, D), torch.float32)
+        ops.gemm_grouped(act, self.w_down, y, *plan)
+        ops.routed_combine(stream.resolve(), y, pair_row, weight, top)
+        if self.shared is not None:
+            self.shared.forward(h, stream, "shared_expert")

@@ -40,6 +40,9 @@ class Model:
         self._readers = {e.reads_cache_of for e in self.run_order if e.reads_cache_of is not None}
         self._last_reader = {e.reads_cache_of: i for i, e in enumerate(self.run_order)
                              if e.reads_cache_of is not None}
+        self._keeps_embedding = any(e.adds_embedding for e in self.run_order)
+        # for inspection and tests: called as tap(run entry index, stream) after every entry
+        self.tap = None
 
     # -- weights -------------------------------------------------------------
     def _bound_parts(self):
@@ -78,6 +81,9 @@ class Model:
         mixer may declare one need or several by name; entries that read another
         entry's cache own none."""
         needs = {}
+        embedding_need = getattr(self.embedding, "cache_need", lambda: None)()
+        for nname, need in normalise_needs(embedding_need).items():
+            needs[(-1, "embedding", nname)] = need           # sorts before every run entry
         for i, e in enumerate(self.run_order):
             if e.reads_cache_of is not None:
                 continue
@@ -123,7 +129,7 @@ class Model:
                 n = len(contexts) * int(need.shape[-1])      # an untied table is read by rows only
             elif name == table_name:
                 n += len(contexts) * int(need.shape[-1])
-            total += n * (4 if need.init == "ones" else esz)
+            total += n * (4 if need.init in ("ones", "around_zero") else esz)
         for e in self.run_order:
             for mixer in self.layers[e.layer].mixers().values():
                 f = getattr(mixer, "cache_read_bytes", None)
@@ -168,7 +174,14 @@ class Model:
         returns float32 logits [n_want, vocab] (None when nothing is wanted).
         Positions are NOT advanced here (the step function does that)."""
         rt = self.rt
-        x = self.embedding.forward(batch)
+        emb_views = {n: cache.view((-1, "embedding", n)) for n in normalise_needs(
+            getattr(self.embedding, "cache_need", lambda: None)())}
+        emb_view = None if not emb_views else (emb_views["cache"] if list(emb_views) == ["cache"]
+                                               else emb_views)
+        x = self.embedding.forward(batch, emb_view, keep_copy=self._keeps_embedding)
+        x0 = None
+        if self._keeps_embedding:
+            x, x0 = x
         stream = ResidualStream(rt, x)
         views = {}
         deferred: Dict[int, list] = {}      # run entry -> cache writes to make once it has run
@@ -177,12 +190,16 @@ class Model:
             owner = i if e.reads_cache_of is None else e.reads_cache_of
             if owner not in views:
                 views[owner] = self._views_of(owner, batch, cache)
+            if e.adds_embedding:
+                stream.add_tensor(x0)
             later = layer.forward(stream, batch, views[owner], shared=e.reads_cache_of is not None)
             if later is not None:
                 # a write the mixer may only make after every entry that reads its cache
                 deferred.setdefault(self._last_reader.get(i, i), []).append(later)
             for write in deferred.pop(i, []):
                 write()
+            if self.tap is not None:
+                self.tap(i, stream)
         if n_want == 0:
             return None
         h = self.final_norm(stream, rows=want_rows, n_rows=n_want, name="final_normed")

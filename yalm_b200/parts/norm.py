@@ -1,6 +1,7 @@
 """RMSNorm: o = x * w / sqrt(mean(x^2) + eps), all in 32 bits; the weight
 multiplies (no 1 + w), as the reference computes it (infer.cpp:136-146,
-infer.cu:525-539)."""
+infer.cu:525-539).  With ``unit_offset`` the stored weight lies around zero and the norm
+multiplies by 1 + w; the sum is formed once, in 32 bits, when the weight is bound."""
 from __future__ import annotations
 
 from typing import Optional
@@ -18,13 +19,16 @@ class RMSNorm:
         self.rt = rt
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.unit_offset = bool(params.get("unit_offset", False))
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_needs(self):
-        return {"weight": TensorNeed((self.size,), init="ones")}
+        return {"weight": TensorNeed((self.size,), init="around_zero" if self.unit_offset else "ones")}
 
     def bind(self, tensors) -> None:
         self.weight = self.rt.vector(tensors["weight"])
+        if self.unit_offset:
+            self.weight = self.weight + 1.0
 
     def __call__(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None,
                  n_rows: Optional[int] = None, name: str = "normed") -> torch.Tensor:

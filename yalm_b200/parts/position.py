@@ -41,6 +41,31 @@ def llama3_inv_freq(head_dim: int, theta: float, scaling: Optional[dict]) -> tor
     return torch.tensor(out, dtype=torch.float64).to(torch.float32)
 
 
+@register_position("none")
+class NoPosition:
+    """No position encoding: q and k stay as projected.  It runs the rotary kernels with every
+    frequency zero (cos 1, sin 0: each rotated pair is exactly the pair that went in), so the
+    same fused paths -- the q/k/v product that stores in its epilogue, the decode attention
+    that sums the product's slices and writes the cache row -- serve a mixer without
+    positions."""
+
+    def __init__(self, params: dict, rt):
+        self.rt = rt
+        self.head_dim = int(params["head_dim"])
+        if self.head_dim % 2:
+            raise ValueError(f"the store kernels take an even head size, got {self.head_dim}")
+        self.inv_freq = torch.zeros(self.head_dim // 2, dtype=torch.float32, device=rt.device)
+        self._table_key = "rope_table_identity_%d" % self.head_dim
+
+    step_table = None              # set below: the same table logic as Rope's
+
+    def rotate_and_store(self, qkv, n_partials, batch, view, q_out, kv_step, H, G,
+                         write_cache=True) -> None:
+        ops.rope_store(qkv, n_partials, self.inv_freq, batch, q_out, kv_step, view.k, view.v,
+                       view.slot_pos, H, G, self.head_dim, view.capacity, write_cache,
+                       pages=view.pages)
+
+
 @register_position("rope")
 class Rope:
     def __init__(self, params: dict, rt):
@@ -73,3 +98,6 @@ class Rope:
         ops.rope_store(qkv, n_partials, self.inv_freq, batch, q_out, kv_step, view.k, view.v,
                        view.slot_pos, H, G, self.head_dim, view.capacity, write_cache,
                        pages=view.pages)
+
+
+NoPosition.step_table = Rope.step_table

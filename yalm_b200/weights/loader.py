@@ -31,7 +31,8 @@ class WeightsError(ValueError):
 @dataclass(frozen=True)
 class TensorNeed:
     """What a part declares about one of its tensors.  ``init`` is used by the
-    random-weights mode: 'normal' (N(0, std)) or 'ones' (1 + N(0, jitter))."""
+    random-weights mode: 'normal' (N(0, std)), 'ones' (1 + N(0, jitter)) or 'around_zero'
+    (N(0, jitter), a norm weight that is stored without its 1)."""
     shape: Tuple[int, ...]
     init: str = "normal"
 

@@ -27,8 +27,9 @@ def random_tensors(needs: Dict[str, TensorNeed], seed: int, dtype: torch.dtype =
     out: Dict[str, torch.Tensor] = {}
     for name in sorted(needs):
         need = needs[name]
-        if need.init == "ones":
-            t = torch.ones(need.shape, dtype=torch.float32, device=device)
+        if need.init in ("ones", "around_zero"):
+            t = torch.full(need.shape, 1.0 if need.init == "ones" else 0.0, dtype=torch.float32,
+                           device=device)
             if norm_jitter:
                 t += norm_jitter * torch.randn(need.shape, generator=gen, dtype=torch.float32,
                                                device=device)
