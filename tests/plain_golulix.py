@@ -87,31 +87,44 @@ def plain_expert(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, limit: flo
 
 
 def plain_route(z: torch.Tensor, r: dict):
-    """z: [T, E] router logits.  Returns (chosen [T, top] long, weights [T, top])."""
+    """z: [T, E] router logits.  Returns (chosen [T, top] long, weights [T, top], margin [T]):
+    margin is how far, relative to the score that was taken last, the nearest score that was
+    not taken lies from it (a group's or an expert's): a small margin is a close call."""
     E, top = int(r["experts"]), int(r["top"])
     s = torch.softmax(z.float(), -1)
     groups = r.get("groups") or {"count": 1, "keep": 1}
     n_g, keep = int(groups["count"]), int(groups["keep"])
     per = E // n_g
     best = s.view(-1, n_g, per).max(-1).values                           # [T, n_g]
+    ranked = best.sort(-1, descending=True).values
+    margin = torch.full((s.shape[0],), float("inf"))
+    if keep < n_g:
+        margin = (ranked[:, keep - 1] - ranked[:, keep]) / ranked[:, keep - 1]
     chosen_groups = best.topk(keep, -1).indices
     allowed = torch.zeros_like(best, dtype=torch.bool).scatter_(1, chosen_groups, True)
     allowed = allowed[:, :, None].expand(-1, -1, per).reshape(-1, E)
     masked = s.masked_fill(~allowed, float("-inf"))
-    idx = masked.topk(top, -1).indices
-    return idx, s.gather(1, idx)
+    order = masked.sort(-1, descending=True)
+    idx = order.indices[:, :top]
+    if top < keep * per:
+        margin = torch.minimum(margin, (order.values[:, top - 1] - order.values[:, top]) / order.values[:, top - 1])
+    return idx, s.gather(1, idx), margin
 
 
-def plain_moe(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict) -> torch.Tensor:
+def plain_moe(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict,
+              margins: Optional[list] = None) -> torch.Tensor:
     r = mlp["router"]
     z = h @ w[f"{p}.router"].float().T
-    idx, wt = plain_route(z, r)
+    idx, wt, margin = plain_route(z, r)
+    if margins is not None:
+        margins.append(margin)
     out = torch.zeros(h.shape[0], w[f"{p}.e0.down"].shape[0])
     limit = float(mlp["expert"]["limit"])
-    for t in range(h.shape[0]):
+    for e in range(int(r["experts"])):
         for j in range(idx.shape[1]):
-            e = int(idx[t, j])
-            out[t] += wt[t, j] * plain_expert(h[t:t + 1], w, f"{p}.e{e}", limit)[0]
+            rows = (idx[:, j] == e).nonzero()[:, 0]
+            if rows.numel():
+                out[rows] += wt[rows, j, None] * plain_expert(h[rows], w, f"{p}.e{e}", limit)
     if mlp.get("shared"):
         out = out + plain_expert(h, w, f"{p}.shared", float(mlp["shared"]["limit"]))
     return out
@@ -131,9 +144,10 @@ def plain_run_order(cfg: dict):
 
 
 def plain_forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
-                  layers_out: Optional[list] = None) -> torch.Tensor:
+                  layers_out: Optional[list] = None, margins: Optional[list] = None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence; ``layers_out`` collects the residual
-    stream after every layer run."""
+    stream after every layer run, ``margins`` the routing margin [T] of every routed
+    feed-forward that ran."""
     eps = float(cfg["norm"]["eps"])
     x0 = plain_embedding(w, cfg, tokens)
     x = x0.clone()
@@ -145,7 +159,7 @@ def plain_forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
         x = x + plain_attention(plain_norm(x, w[f"l{i}.norm1"], eps), w, f"l{i}.mix", layer["mixer"])
         if layer.get("mlp"):
             assert layer["mlp"]["kind"] == "moe", layer["mlp"]["kind"]
-            x = x + plain_moe(plain_norm(x, w[f"l{i}.norm2"], eps), w, f"l{i}.mlp", layer["mlp"])
+            x = x + plain_moe(plain_norm(x, w[f"l{i}.norm2"], eps), w, f"l{i}.mlp", layer["mlp"], margins)
         if layers_out is not None:
             layers_out.append(x.clone())
     logits = plain_norm(x, w["final.norm"], eps) @ w["head"].float().T
@@ -153,3 +167,13 @@ def plain_forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
     if cap:
         logits = float(cap) * torch.tanh(logits / float(cap))
     return logits
+
+
+def plain_generate_greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], n_new: int) -> List[int]:
+    """Greedy continuation, recomputing the whole sequence for every new token."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(plain_forward(cfg, w, toks)[-1].argmax())
+        out.append(nxt)
+        toks.append(nxt)
+    return out
