@@ -317,6 +317,86 @@ def time_prefill(lm, T, reps, pk):
     return out
 
 
+def golulix_config(width, heads, kv_heads, head_dim, chunk, experts, top, groups, keep, ff, shared_ff,
+                   layers, vocab):
+    """A Golulix configuration with layers of the sizes a served model has (random weights)."""
+    layer = {"type": "attention",
+             "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+                       "scale": head_dim ** -0.5, "mask": {"size": chunk}},
+             "mlp": {"kind": "moe", "expert": {"ff": ff, "limit": 7.0},
+                     "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}},
+                     "shared": {"ff": shared_ff, "limit": 7.0}}}
+    return {"architecture": "Golulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "layers": [layer] * layers, "loop": None, "logit_softcap": 30.0}
+
+
+def dense_twin(width, heads, kv_heads, head_dim, chunk, experts, top, groups, keep, ff, shared_ff, layers,
+               vocab):
+    """The closest model the library had before: the Llama / Mistral decoder with the same width,
+    heads and layers, a sliding window of the chunk's size, and a feed-forward as wide as the
+    experts one token uses (top x ff + the shared expert)."""
+    return {"architectures": ["MistralForCausalLM"], "hidden_size": width,
+            "intermediate_size": top * ff + shared_ff, "num_hidden_layers": layers,
+            "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": head_dim,
+            "vocab_size": vocab, "max_position_embeddings": 32768, "rms_norm_eps": 1e-6,
+            "rope_theta": 10000.0, "sliding_window": chunk, "tie_word_embeddings": False,
+            "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2}
+
+
+# name -> sizes (see golulix_config); two shapes of served mixture-of-experts models, cut to a few layers
+DESIGN_SIZES = {
+    "w2048-e32-top4": dict(width=2048, heads=16, kv_heads=4, head_dim=128, chunk=1024, experts=32, top=4,
+                           groups=4, keep=2, ff=768, shared_ff=1536, layers=6, vocab=32000),
+    "w4096-e64-top6": dict(width=4096, heads=32, kv_heads=8, head_dim=128, chunk=2048, experts=64, top=6,
+                           groups=8, keep=4, ff=1024, shared_ff=2048, layers=4, vocab=32000),
+}
+
+
+def compare_designs(args, pk):
+    """Prefill and decode of the Golulix design beside the dense decoder at equal sizes: tokens/s,
+    and how far each is from its roofline (prefill: floating-point operations over the measured
+    matrix-product peak; decode: bytes that must be read over the measured copy rate)."""
+    import torch
+    from yalm_b200 import LM
+    out = {"compare": "golulix vs the dense decoder at equal sizes", "dtype": args.dtype,
+           "peaks": pk["source"], "sizes": {}}
+    names = [args.design_size] if args.design_size else list(DESIGN_SIZES)
+    for name in names:
+        sizes = DESIGN_SIZES[name]
+        rec = {}
+        for who, cfg in (("golulix", golulix_config(**sizes)), ("dense", dense_twin(**sizes))):
+            lm = LM.from_random(cfg, seed=0, dtype=args.dtype, std=0.02, norm_jitter=0.0,
+                                max_context=4096, max_batch=64)
+            torch.cuda.synchronize()
+            r = {"weights_gb": lm.model.weight_bytes() / 1e9}
+            for T in (512, 2048):
+                p = time_prefill(lm, T, 3, pk)
+                # the step's bound: its operations at the matrix-product peak, or its weights (every
+                # expert the tokens reach) at the copy rate, whichever takes longer
+                t_flops = prefill_flops(lm, T) / (pk["bf16_tflops"] * 1e12)
+                t_bytes = lm.model.step_bytes([1] * T) / (pk["hbm_gbs"] * 1e9)
+                r[f"prefill_{T}"] = {"tokens_s": p["value"], "ms": p["ms"], "flops_frac": p["frac"],
+                                     "bound": "flops" if t_flops >= t_bytes else "hbm",
+                                     "roofline_frac": max(t_flops, t_bytes) / (p["ms"] / 1e3)}
+            for b in (8, 64):
+                d = time_decode(lm, b, max(16, args.steps // 2), STEADY, seed=3, lo=64, hi=1500)
+                by = decode_bytes(lm, d["contexts"])
+                r[f"decode_b{b}"] = {"tokens_s": d["tok_s"], "ms": d["ms_per_step"], "launches_per_step":
+                                     d["launches"] / max(16, args.steps // 2),
+                                     "hbm_frac": by / (d["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]}
+            rec[who] = r
+            del lm
+            torch.cuda.empty_cache()
+        rec["roofline_distance_ratio"] = {
+            k: (rec["dense"][k].get("roofline_frac") or rec["dense"][k]["hbm_frac"]) /
+               (rec["golulix"][k].get("roofline_frac") or rec["golulix"][k]["hbm_frac"])
+            for k in rec["golulix"] if k != "weights_gb"}
+        out["sizes"][name] = rec
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm(args):
     """The unmodified reference on the same layer sizes (see baseline/run_reference.py).
     It serves one sequence at a time, so the batch's requests run one after another and
@@ -403,6 +483,11 @@ def main():
     ap.add_argument("--decode-warps", type=int, default=None, choices=[2, 4],
                     help="warps per block of the tensor-core decode attention (default: the "
                          "attention part decides by the batch)")
+    ap.add_argument("--compare-designs", action="store_true",
+                    help="instead of the default workload: prefill and decode of the Golulix design "
+                         "beside the dense decoder at equal sizes (random weights, a few layers)")
+    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES),
+                    help="with --compare-designs: one of the sizes instead of all")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -414,6 +499,8 @@ def main():
     import torch
     from yalm_b200 import LM
     pk = peaks()
+    if args.compare_designs:
+        return compare_designs(args, pk)
     base_cfg, context, default_batch, lo, hi = WORKLOADS[args.workload]
     args.batch = args.batch or default_batch
     args.layers = args.layers or base_cfg["num_hidden_layers"]

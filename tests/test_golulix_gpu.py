@@ -143,15 +143,19 @@ def test_router_choice_plan_and_weights(ops, E, groups, keep, top):
     counts.zero_()
 
 
-@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-def test_grouped_products_activation_and_weighted_sum(ops, dt):
+@pytest.mark.parametrize("dt, tile", [(torch.float32, 0), (torch.bfloat16, 0), (torch.bfloat16, 16),
+                                      (torch.float16, 32), (torch.bfloat16, 64), (torch.float16, 128), (torch.bfloat16, 256)])
+def test_grouped_products_activation_and_weighted_sum(ops, dt, tile):
+    """The routed feed-forward's kernels after the router: plan, gather, grouped gate/up product,
+    clamped activation, grouped down product, weighted sum -- on the FMA kernel (tile 0) and on
+    tcgen05 with every tile size; one expert has many rows (several tiles), one has none."""
     g = torch.Generator().manual_seed(5)
-    n, D, F, E, top = 150, 72, 40, 5, 2
+    n, D, F, E, top = 150, (264 if tile >= 128 else 72), 40, 5, 2       # 264: blocks of 256 features
     h = torch.randn(n, D, generator=g).to(dt)
     wgu = (0.2 * torch.randn(E, 2 * F, D, generator=g)).to(dt)
     wd = (0.2 * torch.randn(E, D, F, generator=g)).to(dt)
     choice = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(n)]).to(torch.int32)
-    choice[:40] = torch.tensor([3, 1], dtype=torch.int32)          # one expert with many rows, one with none
+    choice[:40] = torch.tensor([3, 1], dtype=torch.int32)
     choice[choice == 4] = 0
     choice[:, 1] = torch.where(choice[:, 1] == choice[:, 0], (choice[:, 0] + 1) % 4, choice[:, 1])
     weight = torch.rand(n, top, generator=g)
@@ -167,23 +171,31 @@ def test_grouped_products_activation_and_weighted_sum(ops, dt):
                 y = y.to(dt).float()
             ref[t] += weight[t, j] * (y @ wd[e].float().T)
     i32 = dict(dtype=torch.int32, device=DEV)
-    pairs, mt = n * top, ops.routed_max_tiles(n * top, E)
+    rows_per_tile = tile or ops.ROUTED_TILE
+    pairs, mt = n * top, ops.routed_max_tiles(n * top, E, rows_per_tile)
     counts = torch.bincount(choice.reshape(-1).long(), minlength=E).to(torch.int32).to(DEV)
     first, pair_row, row_token = torch.zeros(E + 1, **i32), torch.zeros(pairs, **i32), torch.zeros(pairs, **i32)
     tile_e, tile_r0, n_tiles = torch.zeros(mt, **i32), torch.zeros(mt, **i32), torch.zeros(1, **i32)
     ops.route_plan(counts, choice.reshape(-1).to(DEV), pairs, top, E, first, pair_row, row_token, tile_e,
-                   tile_r0, n_tiles)
+                   tile_r0, n_tiles, tile_rows=rows_per_tile)
+    plan = (first, tile_e, tile_r0, n_tiles, mt)
     rows = torch.empty(pairs, D, dtype=dt, device=DEV)
     ops.gather_rows(h.to(DEV), row_token, rows)
-    gu = torch.empty(pairs, 2 * F, device=DEV)
-    ops.gemm_grouped(rows, wgu.to(DEV), gu, first, tile_e, tile_r0, n_tiles, mt)
-    act = torch.empty(pairs, F, dtype=dt, device=DEV)
-    ops.glu_clamp(gu, act, 1, 1.702, 1.1, 1.0)
-    y = torch.empty(pairs, D, device=DEV)
-    ops.gemm_grouped(act, wd.to(DEV), y, first, tile_e, tile_r0, n_tiles, mt)
+    act = torch.full((pairs, F), float("nan"), dtype=dt, device=DEV)
+    y = torch.full((pairs, D), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    if tile:
+        ops.gemm_grouped_tc(rows, wgu.to(DEV), act, *plan, tile, status, glu=(1.702, 1.1, 1.0))
+        ops.gemm_grouped_tc(act, wd.to(DEV), y, *plan, tile, status)
+    else:
+        gu = torch.empty(pairs, 2 * F, device=DEV)
+        ops.gemm_grouped(rows, wgu.to(DEV), gu, *plan)
+        ops.glu_clamp(gu, act, 1, 1.702, 1.1, 1.0)
+        ops.gemm_grouped(act, wd.to(DEV), y, *plan)
     xd = x.to(DEV)
     ops.routed_combine(xd, y, pair_row, weight.reshape(-1).to(DEV), top)
-    tol = 2e-5 if dt == torch.float32 else 2e-2
+    assert status.item() == 0
+    tol = 2e-5 if dt == torch.float32 else (2e-2 if dt == torch.bfloat16 else 3e-3)
     assert (xd.cpu() - ref).abs().max().item() <= tol * ref.abs().max().item()
 
 

@@ -140,6 +140,10 @@ class GolulixConfig:
 
     architecture = "Golulix"
 
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "GolulixConfig":
         layers = []

@@ -197,6 +197,13 @@ int yalm_gather_rows(const void* src, const int* row_token, void* dst, int dtype
 int yalm_gemm_grouped(const void* A, int a_dtype, const void* W, int w_dtype, void* out, int out_dtype,
                       const int* first_row, const int* tile_expert, const int* tile_row0,
                       const int* n_tiles, int max_tiles, int N, int K, cudaStream_t stream);
+// the same product on tcgen05 (gemm_tcgen05.cu): 16-bit operands, a plan of tile_rows-row tiles
+// (16, 32, 64 or 128); mode 0 stores the product, mode 2 the gated activation of W = [gate; up]
+int yalm_gemm_grouped_tc(const void* A, const void* W, int ab_dtype, void* out, int out_dtype,
+                         int rows_total, int E, int N, int K, int mode, int tile_rows,
+                         const int* first_row, const int* tile_expert, const int* tile_row0,
+                         const int* n_tiles, int max_tiles, float slope, float limit, float shift,
+                         int* status, cudaStream_t stream);
 int yalm_glu_clamp(const float* gu, int n_partials, long long partial_stride, void* out, int out_dtype,
                    long long rows, int F, float alpha, float limit, float shift, cudaStream_t stream);
 int yalm_routed_combine(float* x, const float* y, const int* pair_row, const float* weight,

@@ -142,6 +142,21 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return scratch[32];
 }
 
+// Sum of the n_partials slices of a split-K product at one element, eight loads in flight at a
+// time (a plain loop would wait for each load before it issues the next).
+__device__ __forceinline__ float sum_slices(const float* __restrict__ p, int n_partials,
+                                            long long partial_stride) {
+  float v = 0.f;
+  for (int s0 = 0; s0 < n_partials; s0 += 8) {
+    float t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = s0 + j < n_partials ? p[(size_t)(s0 + j) * partial_stride] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v += t[j];
+  }
+  return v;
+}
+
 // ---- the rotation of one pair ----------------------------------------------
 // (a, b) -> (a c - b s, a s + b c) with the roundings spelled out, so that every kernel
 // that rotates gives the same bits whatever the compiler would have fused.

@@ -88,6 +88,8 @@ _SIGNATURES = {
     "yalm_gather_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "yalm_gemm_grouped": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "yalm_glu_clamp": [_vp, _i, _ll, _vp, _i, _ll, _i, _f, _f, _f, _vp],
+    "yalm_gemm_grouped_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _f, _f,
+                             _f, _vp, _vp],
     "yalm_routed_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
 }
 
@@ -645,7 +647,8 @@ def route_topk(z: torch.Tensor, n_partials: int, n_tokens: int, E: int, n_groups
 
 
 def routed_max_tiles(n_pairs: int, E: int, tile_rows: int = ROUTED_TILE) -> int:
-    return -(-n_pairs // tile_rows) + E
+    """The most tiles a plan can have: every expert may end with a tile that is not full."""
+    return min(n_pairs, -(-n_pairs // tile_rows) + E)
 
 
 def route_plan(counts, choice, n_pairs: int, top: int, E: int, first_row, pair_row, row_token,
@@ -680,6 +683,36 @@ def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, first_row,
                                    dtype_code(out.dtype), _p(first_row), _p(tile_expert),
                                    _p(tile_row0), _p(n_tiles), max_tiles, N, K, _stream()),
            "gemm_grouped")
+
+
+def routed_tile_rows(n_pairs: int, E: int) -> int:
+    """Rows per tile of the tensor-core grouped product for a step's (token, choice) pairs: the
+    smallest of 16, 32, 64 that holds an expert's share if the pairs spread evenly, else 128
+    (the kernel also takes 256, which was measured and is no faster)."""
+    share = -(-n_pairs // E)
+    for bt in (16, 32, 64):
+        if share <= bt:
+            return bt
+    return 128
+
+
+def gemm_grouped_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, first_row, tile_expert,
+                    tile_row0, n_tiles, max_tiles: int, tile_rows: int, status: torch.Tensor,
+                    glu: Optional[tuple] = None) -> None:
+    """The grouped product on tcgen05: out[r] = a[r] @ w[e].T over a plan of ``tile_rows``-row
+    tiles; with ``glu`` = (slope, limit, shift) and w = [gate; up] per expert, out [rows, N / 2] is
+    the gated activation g' sigmoid(slope g') (u' + shift) under the clamps of ``glu_clamp``."""
+    rows, K = a.shape
+    E, N, _ = w.shape
+    _need(a.dtype == w.dtype and a.dtype in HALF_TYPES and w.shape[2] == K and a.is_contiguous()
+          and w.is_contiguous() and out.is_contiguous(), "gemm_grouped_tc: operands")
+    _need(tuple(out.shape) == (rows, N // 2 if glu else N), "gemm_grouped_tc: out shape")
+    slope, limit, shift = glu if glu else (1.0, 0.0, 0.0)
+    _check(lib().yalm_gemm_grouped_tc(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype),
+                                      rows, E, N, K, 2 if glu else 0, tile_rows, _p(first_row),
+                                      _p(tile_expert), _p(tile_row0), _p(n_tiles), max_tiles,
+                                      float(slope), float(limit), float(shift), _p(status), _stream()),
+           "gemm_grouped_tc")
 
 
 def glu_clamp(gu: torch.Tensor, out: torch.Tensor, n_partials: int, alpha: float, limit: float,

@@ -44,8 +44,7 @@ route_topk_kernel(const float* __restrict__ z, int n_partials, long long partial
 
   float m = -INFINITY;
   for (int e = lane; e < E; e += 32) {
-    float v = 0.f;
-    for (int s = 0; s < n_partials; ++s) v += z[(size_t)s * partial_stride + (size_t)t * E + e];
+    const float v = sum_slices(z + (size_t)t * E + e, n_partials, partial_stride);
     score[e] = v;
     m = fmaxf(m, v);
   }
@@ -233,30 +232,43 @@ gemm_grouped_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
   }
 }
 
-// gu [S][rows][2F] float32 (gate columns, then up columns) -> out [rows][F]
-template <typename TO>
+// gu [S][rows][2F] float32 (gate columns, then up columns) -> out [rows][F]; a block row per
+// matrix row (blockIdx.x), VEC features per thread (4 when F is a multiple of 4)
+template <typename TO, int VEC>
 __global__ void glu_clamp_kernel(const float* __restrict__ gu, int n_partials, long long partial_stride,
-                                 TO* __restrict__ out, long long total, int F, float alpha, float limit,
-                                 float shift) {
+                                 TO* __restrict__ out, int F, float alpha, float limit, float shift) {
   pdl_launch_dependents();
   pdl_wait();
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const long long r = i / F;
-  const int f = (int)(i % F);
-  float g = 0.f, u = 0.f;
+  const size_t r = blockIdx.x;
+  const int f = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (f >= F) return;
+  const float* p = gu + r * 2 * F + f;
+  float g[VEC], u[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) { g[v] = 0.f; u[v] = 0.f; }
   for (int s = 0; s < n_partials; ++s) {
-    const float* p = gu + (size_t)s * partial_stride + (size_t)r * 2 * F;
-    g += p[f];
-    u += p[F + f];
+    const float* q = p + (size_t)s * partial_stride;
+    if (VEC == 4) {
+      const float4 a = *reinterpret_cast<const float4*>(q), b = *reinterpret_cast<const float4*>(q + F);
+      g[0] += a.x; g[VEC > 1 ? 1 : 0] += a.y; g[VEC > 2 ? 2 : 0] += a.z; g[VEC > 3 ? 3 : 0] += a.w;
+      u[0] += b.x; u[VEC > 1 ? 1 : 0] += b.y; u[VEC > 2 ? 2 : 0] += b.z; u[VEC > 3 ? 3 : 0] += b.w;
+    } else {
+      g[0] += q[0];
+      u[0] += q[F];
+    }
   }
-  if (limit > 0.f) {
-    g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    float gg = g[v], uu = u[v];
+    if (limit > 0.f) {
+      gg = fminf(gg, limit);
+      uu = fminf(fmaxf(uu, -limit), limit);
+    }
+    out[r * F + f + v] = from_float<TO>(gg * (1.0f / (1.0f + expf(-alpha * gg))) * (uu + shift));
   }
-  const float y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift);
-  out[i] = from_float<TO>(y);
 }
+
+constexpr int RC_MAX_TOP = 256;
 
 __global__ void routed_combine_kernel(float* __restrict__ x, const float* __restrict__ y,
                                       const int* __restrict__ pair_row, const float* __restrict__ weight,
@@ -264,10 +276,45 @@ __global__ void routed_combine_kernel(float* __restrict__ x, const float* __rest
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
+  __shared__ int row_s[RC_MAX_TOP];
+  __shared__ float w_s[RC_MAX_TOP];
+  for (int j = threadIdx.x; j < top; j += blockDim.x) {
+    row_s[j] = pair_row[(size_t)t * top + j];
+    w_s[j] = weight[(size_t)t * top + j];
+  }
+  __syncthreads();
+  // the rows of up to eight choices are loaded together, then added in the order of the choices
+  if (dim % 4 == 0) {
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(x + (size_t)t * dim + i);
+      for (int j0 = 0; j0 < top; j0 += 8) {
+        float4 r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          r[j] = j0 + j < top ? *reinterpret_cast<const float4*>(y + (size_t)row_s[j0 + j] * dim + i)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j0 + j < top) {
+            const float w = w_s[j0 + j];
+            v.x = fmaf(w, r[j].x, v.x); v.y = fmaf(w, r[j].y, v.y);
+            v.z = fmaf(w, r[j].z, v.z); v.w = fmaf(w, r[j].w, v.w);
+          }
+      }
+      *reinterpret_cast<float4*>(x + (size_t)t * dim + i) = v;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
     float v = x[(size_t)t * dim + i];
-    for (int j = 0; j < top; ++j)
-      v = fmaf(weight[(size_t)t * top + j], y[(size_t)pair_row[(size_t)t * top + j] * dim + i], v);
+    for (int j0 = 0; j0 < top; j0 += 8) {
+      float r[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) r[j] = j0 + j < top ? y[(size_t)row_s[j0 + j] * dim + i] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j0 + j < top) v = fmaf(w_s[j0 + j], r[j], v);
+    }
     x[(size_t)t * dim + i] = v;
   }
 }
@@ -369,13 +416,19 @@ extern "C" int yalm_gemm_grouped(const void* A, int a_dtype, const void* W, int 
 extern "C" int yalm_glu_clamp(const float* gu, int n_partials, long long partial_stride, void* out,
                               int out_dtype, long long rows, int F, float alpha, float limit, float shift,
                               cudaStream_t stream) {
-  const long long total = rows * F;
-  if (total <= 0) return 0;
-  const long long blocks = (total + 255) / 256;
-  if (blocks > 0x7fffffffLL) return -4;
+  if (rows <= 0 || F <= 0) return 0;
+  if (rows > 0x7fffffffLL) return -4;
+  const bool vec = F % 4 == 0 && partial_stride % 4 == 0 && ((uintptr_t)gu & 15) == 0;
+  const int per_block = 128 * (vec ? 4 : 1);
+  const dim3 grid((unsigned)rows, (F + per_block - 1) / per_block);
+  if (grid.y > 65535) return -4;
 #define YALM_GC(TO)                                                                                  \
-  launch_pdl(glu_clamp_kernel<TO>, dim3((unsigned)blocks), dim3(256), 0, stream, gu, n_partials,     \
-             partial_stride, (TO*)out, total, F, alpha, limit, shift)
+  do {                                                                                               \
+    if (vec) launch_pdl(glu_clamp_kernel<TO, 4>, grid, dim3(128), 0, stream, gu, n_partials,         \
+                        partial_stride, (TO*)out, F, alpha, limit, shift);                           \
+    else launch_pdl(glu_clamp_kernel<TO, 1>, grid, dim3(128), 0, stream, gu, n_partials,             \
+                    partial_stride, (TO*)out, F, alpha, limit, shift);                               \
+  } while (0)
   if (out_dtype == DT_F32) YALM_GC(float);
   else if (out_dtype == DT_BF16) YALM_GC(__nv_bfloat16);
   else if (out_dtype == DT_F16) YALM_GC(__half);
@@ -388,6 +441,7 @@ extern "C" int yalm_glu_clamp(const float* gu, int n_partials, long long partial
 extern "C" int yalm_routed_combine(float* x, const float* y, const int* pair_row, const float* weight,
                                    int n_tokens, int top, int dim, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (top <= 0 || top > RC_MAX_TOP) return -2;
   launch_pdl(routed_combine_kernel, dim3(n_tokens), dim3(dim >= 1024 ? 256 : 128), 0, stream, x, y,
              pair_row, weight, top, dim);
   YALM_LAUNCH_CHECK();

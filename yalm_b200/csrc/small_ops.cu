@@ -64,12 +64,23 @@ __global__ void head_gate_kernel(T* __restrict__ o, const float* __restrict__ g,
   extern __shared__ float gate_s[];
   const int t = blockIdx.x;
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    float z = 0.f;
-    for (int s = 0; s < n_partials; ++s) z += g[(size_t)s * partial_stride + (size_t)t * H + h];
+    const float z = sum_slices(g + (size_t)t * H + h, n_partials, partial_stride);
     gate_s[h] = 1.0f / (1.0f + expf(-z));
   }
   __syncthreads();
   T* row = o + (size_t)t * H * hd;
+  // a thread takes whole runs of 8 elements of one head where the head size allows it
+  if (hd % 8 == 0 && sizeof(T) == 2) {
+    for (int i = threadIdx.x * 8; i < H * hd; i += blockDim.x * 8) {
+      const float gt = gate_s[i / hd];
+      uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+      T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = from_float<T>(to_float(e[j]) * gt);
+      *reinterpret_cast<uint4*>(row + i) = raw;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H * hd; i += blockDim.x)
     row[i] = from_float<T>(to_float(row[i]) * gate_s[i / hd]);
 }
@@ -88,8 +99,7 @@ __global__ void residual_add_kernel(float* __restrict__ x, const float* __restri
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  float v = x[i];
-  for (int s = 0; s < n_partials; ++s) v += partials[(size_t)s * partial_stride + i];
+  const float v = x[i] + (n_partials ? sum_slices(partials + i, n_partials, partial_stride) : 0.f);
   x[i] = v + y[i];
 }
 

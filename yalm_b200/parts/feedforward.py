@@ -145,6 +145,16 @@ class RoutedExperts:
         if self.shared is not None:
             self.shared.bind(tensors["shared.gate"], tensors["shared.up"], tensors["shared.down"])
 
+    def step_weight_bytes(self, n_tokens: int, element_size: int) -> int:
+        """Weight bytes a step of ``n_tokens`` tokens reads: the router, the shared expert, and the
+        experts the tokens reach -- as many as independent, evenly spread choices reach on
+        average, E (1 - (1 - top/E)^n)."""
+        hit = self.E * (1.0 - (1.0 - self.top / self.E) ** n_tokens)
+        n = self.E * self.D + int(hit * 3 * self.F * self.D)
+        if self.shared is not None:
+            n += 3 * self.shared.F * self.D
+        return n * element_size
+
     def flops(self, q_lens, past) -> float:
         n = sum(q_lens)
         total = 2.0 * n * (self.E * self.D + self.top * 3 * self.F * self.D)
@@ -161,7 +171,12 @@ class RoutedExperts:
         weight = rt.buffer("routed_weight", (pairs,), torch.float32)
         counts = rt.zeros("routed_counts", E)
         ops.route_topk(z, S, n, E, self.groups, self.keep, top, self.renormalise, choice, weight, counts)
-        max_tiles = ops.routed_max_tiles(pairs, E)
+        # 16-bit operands that TMA can address: both grouped products on tcgen05, the activation
+        # in the first one's epilogue; else the FMA kernel (the 32-bit path among others)
+        tensor_cores = (rt.gemm != "simt" and h.dtype in ops.HALF_TYPES and self.w_down.dtype == h.dtype
+                        and D % 8 == 0 and F % 8 == 0)
+        tile = ops.routed_tile_rows(pairs, E) if tensor_cores else ops.ROUTED_TILE
+        max_tiles = ops.routed_max_tiles(pairs, E, tile)
         first_row = rt.buffer("routed_first_row", (E + 1,), i32)
         pair_row = rt.buffer("routed_pair_row", (pairs,), i32)
         row_token = rt.buffer("routed_row_token", (pairs,), i32)
@@ -169,16 +184,21 @@ class RoutedExperts:
         tile_row0 = rt.buffer("routed_tile_row0", (max_tiles,), i32)
         n_tiles = rt.buffer("routed_n_tiles", (1,), i32)
         ops.route_plan(counts, choice, pairs, top, E, first_row, pair_row, row_token, tile_expert,
-                       tile_row0, n_tiles)
+                       tile_row0, n_tiles, tile_rows=tile)
         plan = (first_row, tile_expert, tile_row0, n_tiles, max_tiles)
         rows = rt.buffer("routed_rows", (pairs, D), h.dtype)
         ops.gather_rows(h, row_token, rows)
-        gu = rt.buffer("routed_gate_up", (pairs, 2 * F), torch.float32)
-        ops.gemm_grouped(rows, self.w_gate_up, gu, *plan)
         act = rt.buffer("routed_act", (pairs, F), rt.dtype)
-        ops.glu_clamp(gu, act, 1, self.slope, self.limit, self.shift)
         y = rt.buffer("routed_out", (pairs, D), torch.float32)
-        ops.gemm_grouped(act, self.w_down, y, *plan)
+        if tensor_cores:
+            ops.gemm_grouped_tc(rows, self.w_gate_up, act, *plan, tile, rt.status,
+                                glu=(self.slope, self.limit, self.shift))
+            ops.gemm_grouped_tc(act, self.w_down, y, *plan, tile, rt.status)
+        else:
+            gu = rt.buffer("routed_gate_up", (pairs, 2 * F), torch.float32)
+            ops.gemm_grouped(rows, self.w_gate_up, gu, *plan)
+            ops.glu_clamp(gu, act, 1, self.slope, self.limit, self.shift)
+            ops.gemm_grouped(act, self.w_down, y, *plan)
         ops.routed_combine(stream.resolve(), y, pair_row, weight, top)
         if self.shared is not None:
             self.shared.forward(h, stream, "shared_expert")

@@ -121,7 +121,20 @@ class Model:
         table_name = self.spec.embedding.tensors.get("weight")
         tied = table_name in self.spec.head.tensors.values()
         total = 0
+        # a part that reads only some of its weights in a step (routed experts) counts its own
+        own = set()
+        for part, pspec in self._bound_parts():
+            f = getattr(part, "step_weight_bytes", None)
+            if f is not None:
+                own.update(pspec.tensors[key] for key in part.tensor_needs())
+        for e in self.run_order:
+            for part, _ in self.layers[e.layer].parts():
+                f = getattr(part, "step_weight_bytes", None)
+                if f is not None:
+                    total += f(len(contexts), esz)
         for name, need in needs.items():
+            if name in own:
+                continue
             n = 1
             for d in need.shape:
                 n *= int(d)
