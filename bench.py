@@ -327,8 +327,8 @@ def golulix_config(width, heads, kv_heads, head_dim, chunk, experts, top, groups
                      "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}},
                      "shared": {"ff": shared_ff, "limit": 7.0}}}
     return {"architecture": "Golulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
-            "layers": [layer] * layers, "loop": None, "logit_softcap": 30.0}
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 999983}},
+            "layers": [layer] * layers, "loop": None, "logit_softcap": 50.0}
 
 
 def dense_twin(width, heads, kv_heads, head_dim, chunk, experts, top, groups, keep, ff, shared_ff, layers,

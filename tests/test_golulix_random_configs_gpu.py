@@ -42,8 +42,8 @@ def draw(seed):
     start = rng.randint(0, n_layers - 1)
     cfg = {"architecture": "Golulix", "vocab": rng.choice([61, 256, 500]),
            "width": rng.choice([24, 64, 72, 100, 136]), "norm": {"eps": rng.choice([1e-5, 1e-6])},
-           "embedding": {"bigram": {"buckets": rng.choice([1, 17, 4099]), "mul_prev": rng.choice([1, 31, 1000003]),
-                                    "mul_cur": rng.choice([1, 17, 999983])}},
+           "embedding": {"bigram": {"buckets": rng.choice([1, 17, 4099]), "mul_prev": rng.choice([1, 29, 1000003]),
+                                    "mul_cur": rng.choice([1, 13, 999983])}},
            "layers": layers,
            "loop": rng.choice([None, {"start": start, "stop": rng.randint(start + 1, n_layers),
                                       "times": rng.choice([1, 2, 3])}]),
@@ -52,7 +52,9 @@ def draw(seed):
     return cfg, lens, rng.random() < 0.5
 
 
-@pytest.mark.parametrize("seed", list(range(21, 33)))
+# 207, 277, 295: key size 8 in prompts of more than 128 tokens (the q/k/v product's storing
+# epilogue takes head sizes from 16 on; these once went to it)
+@pytest.mark.parametrize("seed", list(range(21, 45)) + [207, 277, 295])
 def test_a_random_configuration_matches_the_plain_model(seed):
     from yalm_b200 import LM
     from yalm_b200.config import config_from_dict

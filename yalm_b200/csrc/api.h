@@ -163,7 +163,7 @@ int yalm_gemm_2sm(const void* A, const void* W, int ab_dtype, void* out, int out
 int yalm_gemm_2sm_token_tile(int M, int N, int splits);
 
 // The q/k/v product of many tokens with rotary encoding and cache write in its epilogue
-// (head sizes that divide 128).
+// (head sizes 16, 32, 64 and 128).
 int yalm_gemm_2sm_rope(const void* A, const void* W, int ab_dtype, int M, int N, int K,
                        const yalm_rope_args* rope, int* status, cudaStream_t stream);
 

@@ -1309,7 +1309,8 @@ extern "C" int yalm_gemm_2sm_rope(const void* A, const void* W, int ab_dtype, in
   if (K <= 0 || K % 8 != 0) return -2;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -6;
   const int hd = rope->hd;
-  if (hd <= 0 || hd % 2 != 0 || TC_BM % hd != 0) return -2;        // a block's 128 rows hold whole heads
+  // a block's 128 rows hold whole heads, and a thread's run of 16 features lies in one head
+  if (hd <= 0 || hd % 16 != 0 || TC_BM % hd != 0) return -2;
   if (N != (rope->H + 2 * rope->G) * hd || rope->capacity <= 0) return -2;
   if (!rope->cos_sin || !rope->token_seq || !rope->q_start || !rope->seq_slot || !rope->slot_pos ||
       !rope->q_out || !rope->kv_step || !rope->k_cache || !rope->v_cache)

@@ -537,8 +537,9 @@ class _RopeArgs(ctypes.Structure):
 
 def gemm_2sm_rope_usable(a: torch.Tensor, w: torch.Tensor, hd: int) -> bool:
     """The q/k/v product with the rotary epilogue takes what the tcgen05 product takes and
-    head sizes that divide 128 (a block's 128 rows then hold whole heads)."""
-    return gemm_tc_usable(a, w) and hd % 2 == 0 and 128 % hd == 0
+    head sizes 16, 32, 64 and 128: a block's 128 rows then hold whole heads, and the 16
+    features a thread stores lie in one head."""
+    return gemm_tc_usable(a, w) and hd % 16 == 0 and 128 % hd == 0
 
 
 def rope_table(inv_freq: torch.Tensor, batch, slot_pos: torch.Tensor, out: torch.Tensor) -> None:
