@@ -199,6 +199,49 @@ def test_grouped_products_activation_and_weighted_sum(ops, dt, tile):
     assert (xd.cpu() - ref).abs().max().item() <= tol * ref.abs().max().item()
 
 
+@pytest.mark.parametrize("dt, eps", HALF)
+@pytest.mark.parametrize("M, F, K", [(5, 64, 72), (40, 208, 256), (130, 96, 64), (300, 256, 136)])
+def test_dense_products_with_the_clamped_activation_in_their_epilogue(ops, dt, eps, M, F, K):
+    """The gate/up product of a dense feed-forward with g' sigmoid(slope g') (u' + shift) under
+    clamps where SiLU(g) u would be: single-SM and two-SM kernels, gate and up rows stacked or
+    interleaved in groups of 16, and the kernel that sums split-K slices, against 32-bit."""
+    g = torch.Generator().manual_seed(M + F)
+    a = torch.randn(M, K, generator=g).to(dt)
+    wg = (0.3 * torch.randn(F, K, generator=g)).to(dt)
+    wu = (0.3 * torch.randn(F, K, generator=g)).to(dt)
+    slope, limit, shift = 1.702, 1.3, 1.0
+    gg = torch.clamp(a.float() @ wg.float().T, max=limit)
+    uu = torch.clamp(a.float() @ wu.float().T, -limit, limit)
+    ref = gg * torch.sigmoid(slope * gg) * (uu + shift)
+    stacked = torch.cat([wg, wu], 0).to(DEV)
+    paired = torch.stack([wg.view(F // 16, 16, K), wu.view(F // 16, 16, K)], 1).reshape(2 * F, K).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ad = a.to(DEV)
+    outs = {}
+    for name, w, mode, pr in (("stacked", stacked, ops.GEMM_SILU_MUL, False), ("paired", paired, ops.GEMM_SILU_PAIRED, True)):
+        o = torch.empty(M, F, dtype=dt, device=DEV)
+        ops.gemm_tc(ad, w, o, mode, status, glu=(slope, limit, shift))
+        outs["single-SM " + name] = o
+        if M > 128:
+            o = torch.empty(M, F, dtype=dt, device=DEV)
+            ops.gemm_2sm(ad, w, o, mode, status, glu=(slope, limit, shift))
+            outs["two-SM " + name] = o
+        S = 2 if K >= 128 else 1
+        parts = torch.empty(S, M, 2 * F, device=DEV)
+        ops.gemm_tc(ad, w, parts, ops.GEMM_SPLIT, status, splits=S)
+        o = torch.empty(M, F, dtype=dt, device=DEV)
+        ops.glu_clamp(parts, o, S, slope, limit, shift, paired=pr)
+        outs["slices summed " + name] = o
+    # SiLU is the case (1, none, 0): the same bits as the kernels' own SiLU epilogue
+    o1, o2 = torch.empty(M, F, dtype=dt, device=DEV), torch.empty(M, F, dtype=dt, device=DEV)
+    ops.gemm_tc(ad, paired, o1, ops.GEMM_SILU_PAIRED, status)
+    ops.gemm_tc(ad, paired, o2, ops.GEMM_SILU_PAIRED, status, glu=(1.0, 0.0, 0.0))
+    assert torch.equal(o1, o2) and status.item() == 0
+    for name, o in outs.items():
+        err = (o.float().cpu() - ref).abs().max().item()
+        assert err <= 4 * eps * max(1.0, ref.abs().max().item()), (name, err)
+
+
 def _chunk_reference(q, k, v, scale, chunk):
     """q [T, H, hd], k, v [T, G, hd] of one sequence -> [T, H, hd], 32-bit, chunk mask."""
     T, H, _ = q.shape

@@ -129,6 +129,15 @@ float yalm_uniform01(unsigned long long seed, unsigned key, unsigned counter);
 // status: a device int that receives ERR_WAIT_TIMEOUT if a bounded wait gave up.
 int yalm_gemm_tc(const void* A, const void* W, int ab_dtype, void* out, int out_dtype, int M,
                  int N, int K, int mode, int splits, int* status, cudaStream_t stream);
+// modes 2 and 4 of yalm_gemm_tc / yalm_gemm_2sm with a gated activation other than SiLU:
+// out = g' sigmoid(slope g') (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit)
+// (no clamps when limit <= 0)
+int yalm_gemm_tc_glu(const void* A, const void* W, int ab_dtype, void* out, int out_dtype, int M,
+                     int N, int K, int mode, float slope, float limit, float shift, int* status,
+                     cudaStream_t stream);
+int yalm_gemm_2sm_glu(const void* A, const void* W, int ab_dtype, void* out, int out_dtype, int M,
+                      int N, int K, int mode, float slope, float limit, float shift, int* status,
+                      cudaStream_t stream);
 // 0 if the driver's tensor-map encoder was found (host-side set-up of yalm_gemm_tc).
 int yalm_gemm_tc_available(void);
 
@@ -205,7 +214,8 @@ int yalm_gemm_grouped_tc(const void* A, const void* W, int ab_dtype, void* out, 
                          const int* n_tiles, int max_tiles, float slope, float limit, float shift,
                          int* status, cudaStream_t stream);
 int yalm_glu_clamp(const float* gu, int n_partials, long long partial_stride, void* out, int out_dtype,
-                   long long rows, int F, float alpha, float limit, float shift, cudaStream_t stream);
+                   long long rows, int F, float alpha, float limit, float shift, int paired,
+                   cudaStream_t stream);
 int yalm_routed_combine(float* x, const float* y, const int* pair_row, const float* weight,
                         int n_tokens, int top, int dim, cudaStream_t stream);
 

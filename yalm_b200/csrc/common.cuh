@@ -76,6 +76,31 @@ __device__ __forceinline__ void silu_pairs_of_chunk(const float* v, int lane, fl
     r[j] = silu_times_fast(lo ? v[j] : got, lo ? got : v[8 + j]);
   }
 }
+// A gated activation with clamps, of which SiLU(g) u is the case slope 1, no limit, shift 0:
+// y = g' sigmoid(slope g') (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit)
+// (no clamps when limit <= 0).  For results that are rounded to a 16-bit type: 2^x and the
+// division are the special-function unit's approximations, as in silu_times_fast, whose bits it
+// gives for the SiLU case.
+struct GluParams { float slope, limit, shift; };
+
+__device__ __forceinline__ float glu_clamped_fast(float g, float u, const GluParams& p) {
+  if (p.limit > 0.f) {
+    g = fminf(g, p.limit);
+    u = fminf(fmaxf(u, -p.limit), p.limit);
+  }
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * p.slope * g));
+  return __fdividef(g * (u + p.shift), 1.0f + e);
+}
+// silu_pairs_of_chunk with that activation
+__device__ __forceinline__ void glu_pairs_of_chunk(const float* v, int lane, float* r, const GluParams& p) {
+  const bool lo = lane < 16;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float got = __shfl_xor_sync(0xffffffffu, lo ? v[8 + j] : v[j], 16);
+    r[j] = glu_clamped_fast(lo ? v[j] : got, lo ? got : v[8 + j], p);
+  }
+}
 // ... and its store: eight tokens from tok_first on (those below M) of feature f, row pitch n_out
 __device__ __forceinline__ void store_eight_tokens(int out_dtype, void* __restrict__ out, const float* r,
                                                    int f, int tok_first, int M, int n_out) {

@@ -113,12 +113,16 @@ template <int BT, int NACC> struct TcCfg {
 };
 
 // mode 0: store, 1: add into float32 out, 2: silu(gate)*up (NACC == 2), 3: split-K partials,
-// 4: silu(gate)*up with gate and up rows interleaved in groups of 16 (out is [M, N/2])
+// 4: silu(gate)*up with gate and up rows interleaved in groups of 16 (out is [M, N/2]).
+// `glu` generalises the activation of modes 2 and 4 (see GluParams; SiLU is {1, 0, 0}).
+// The activation of the call that is being launched: SiLU unless an entry point set another.
+static thread_local GluParams g_glu = {1.f, 0.f, 0.f};
+
 template <int BT, int NACC>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                void* __restrict__ out, int out_dtype, int ab_dtype, int M, int N, int K, int mode,
-               int splits, int* __restrict__ status) {
+               int splits, int* __restrict__ status, const GluParams glu) {
   using Cfg = TcCfg<BT, NACC>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[Cfg::STAGES];
@@ -249,12 +253,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           float u[16];
           tmem_ld16(taddr + BT + c0, u);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = silu_times_fast(v[j], u[j]);
+          for (int j = 0; j < 16; ++j) v[j] = glu_clamped_fast(v[j], u[j], glu);
         }
         if (mode == 4) {
           // weight rows come as 16 gate rows followed by the 16 up rows of the same features
           float r[8];
-          silu_pairs_of_chunk(v, lane, r);
+          glu_pairs_of_chunk(v, lane, r, glu);
           const int fo = (feat0 >> 1) + quarter * 16 + (lane & 15);
           if (fo < (N >> 1))
             store_eight_tokens(out_dtype, out, r, fo, tok0 + c0 + (lane < 16 ? 0 : 8), M, N >> 1);
@@ -375,7 +379,7 @@ static int launch_tc(const CUtensorMap& mw, const void* A, void* out, int out_dt
   const dim3 grid((n_out + TC_BM - 1) / TC_BM, (M + BT - 1) / BT, splits);
   if (grid.y > 65535 || grid.z > 65535) return -4;
   launch_pdl(gemm_tc_kernel<BT, NACC>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, mw, ma, out,
-             out_dtype, ab_dtype, M, N, K, mode, splits, status);
+             out_dtype, ab_dtype, M, N, K, mode, splits, status, g_glu);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -397,18 +401,6 @@ static int launch_tc(const CUtensorMap& mw, const void* A, void* out, int out_dt
 // Token tiles of 256 rows (and blocks of 256 features sharing one token tile) were measured at
 // 12,288 rows of 64 experts, K = 4,096 and 1,024: no faster than tiles of 128 (0.61 against 0.64
 // PFLOP/s); a block's three 64 KiB stages hold no more bytes in flight than six of 32 KiB.
-struct GluParams { float slope, limit, shift; };
-
-__device__ __forceinline__ float glu_clamped_fast(float g, float u, const GluParams& p) {
-  if (p.limit > 0.f) {
-    g = fminf(g, p.limit);
-    u = fminf(fmaxf(u, -p.limit), p.limit);
-  }
-  float e;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * p.slope * g));
-  return __fdividef(g * (u + p.shift), 1.0f + e);
-}
-
 template <int BT, int NACC>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
@@ -683,7 +675,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
 gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                 const __grid_constant__ CUtensorMap map_out, int out_tma,
                 void* __restrict__ out, int out_dtype, int ab_dtype, int M, int N, int K, int mode,
-                int splits, int* __restrict__ status, const yalm_rope_args rope) {
+                int splits, int* __restrict__ status, const yalm_rope_args rope, const GluParams glu) {
   using Cfg = G2Cfg<BT, NACC>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[Cfg::STAGES];
@@ -976,7 +968,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           float v[16];
           tmem_ld16(taddr + c0, v);
           float r[8];
-          silu_pairs_of_chunk(v, lane, r);
+          glu_pairs_of_chunk(v, lane, r, glu);
           const uint32_t st = smem_u32(epi_smem) + (uint32_t)((stage_it & 1) * 16 * 64 * 2);
           if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
@@ -1041,12 +1033,12 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           float g2[16];
           tmem_ld16(taddr + BT + c0, g2);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = silu_times_fast(v[j], g2[j]);
+          for (int j = 0; j < 16; ++j) v[j] = glu_clamped_fast(v[j], g2[j], glu);
         }
         if (mode == 4) {
           // rows interleaved in groups of 16: gate and up of a feature in lanes l and l + 16
           float r[8];
-          silu_pairs_of_chunk(v, lane, r);
+          glu_pairs_of_chunk(v, lane, r, glu);
           const int fo = ((feat0 + (int)rank * TC_BM) >> 1) + quarter * 16 + (lane & 15);
           if (fo < (N >> 1))
             store_eight_tokens(out_dtype, out, r, fo, tok0 + c0 + (lane < 16 ? 0 : 8), M, N >> 1);
@@ -1120,7 +1112,7 @@ static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, in
   if (pairs > tiles * splits) pairs = tiles * splits;
   if (pairs < 1) return -4;
   launch_pdl(gemm_2sm_kernel<BT, NACC, SPLIT>, dim3((unsigned)(2 * pairs)), dim3(TC_THREADS), Cfg::SMEM,
-             stream, mw, ma, mo, out_tma, out, out_dtype, ab_dtype, M, N, K, mode, splits, status, rope);
+             stream, mw, ma, mo, out_tma, out, out_dtype, ab_dtype, M, N, K, mode, splits, status, rope, g_glu);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -1290,6 +1282,27 @@ extern "C" int yalm_gemm_2sm(const void* A, const void* W, int ab_dtype, void* o
   if (two_sm_token_tile(M, N, 1) == 240)
     return launch_2sm<240, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, 1, status, stream, none);
   return launch_2sm<256, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, 1, status, stream, none);
+}
+
+// yalm_gemm_tc / yalm_gemm_2sm in mode 2 or 4 with the gated activation of GluParams in place of
+// SiLU(gate) * up: out = g' sigmoid(slope g') (u' + shift) under the clamps of `limit`.
+extern "C" int yalm_gemm_tc_glu(const void* A, const void* W, int ab_dtype, void* out, int out_dtype,
+                                int M, int N, int K, int mode, float slope, float limit, float shift,
+                                int* status, cudaStream_t stream) {
+  if (mode != 2 && mode != 4) return -3;
+  g_glu = {slope, limit, shift};
+  const int rc = yalm_gemm_tc(A, W, ab_dtype, out, out_dtype, M, N, K, mode, 1, status, stream);
+  g_glu = {1.f, 0.f, 0.f};
+  return rc;
+}
+extern "C" int yalm_gemm_2sm_glu(const void* A, const void* W, int ab_dtype, void* out, int out_dtype,
+                                 int M, int N, int K, int mode, float slope, float limit, float shift,
+                                 int* status, cudaStream_t stream) {
+  if (mode != 2 && mode != 4) return -3;
+  g_glu = {slope, limit, shift};
+  const int rc = yalm_gemm_2sm(A, W, ab_dtype, out, out_dtype, M, N, K, mode, 1, status, stream);
+  g_glu = {1.f, 0.f, 0.f};
+  return rc;
 }
 
 // The token tile that yalm_gemm_2sm takes for these sizes (256 or 240): callers that plan a

@@ -87,7 +87,9 @@ _SIGNATURES = {
     "yalm_route_plan": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "yalm_gather_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "yalm_gemm_grouped": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
-    "yalm_glu_clamp": [_vp, _i, _ll, _vp, _i, _ll, _i, _f, _f, _f, _vp],
+    "yalm_glu_clamp": [_vp, _i, _ll, _vp, _i, _ll, _i, _f, _f, _f, _i, _vp],
+    "yalm_gemm_tc_glu": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _f, _vp, _vp],
+    "yalm_gemm_2sm_glu": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _f, _vp, _vp],
     "yalm_gemm_grouped_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _f, _f,
                              _f, _vp, _vp],
     "yalm_routed_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
@@ -490,7 +492,9 @@ def gemm_tc_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, status: torch.Tensor,
-            splits: int = 1) -> None:
+            splits: int = 1, glu: Optional[tuple] = None) -> None:
+    """``glu`` = (slope, limit, shift): modes GEMM_SILU_MUL and GEMM_SILU_PAIRED compute
+    g' sigmoid(slope g') (u' + shift) under the clamps of ``glu_clamp`` instead of SiLU(g) u."""
     M, K = a.shape
     N = w.shape[0]
     _need(a.dtype == w.dtype and a.dtype in HALF_TYPES and w.shape[1] == K
@@ -501,12 +505,18 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, stat
         _need(out.dtype == torch.float32 and out.numel() >= splits * M * N, "gemm_tc: split scratch")
     else:
         _need(tuple(out.shape) == (M, N), "gemm_tc: out is [M, N]")
+    if glu is not None:
+        _need(mode in (GEMM_SILU_MUL, GEMM_SILU_PAIRED), "gemm_tc: an activation needs a gated mode")
+        _check(lib().yalm_gemm_tc_glu(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype), M,
+                                      N, K, mode, float(glu[0]), float(glu[1]), float(glu[2]), _p(status),
+                                      _stream()), "gemm_tc")
+        return
     _check(lib().yalm_gemm_tc(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype), M,
                               N, K, mode, splits, _p(status), _stream()), "gemm_tc")
 
 
 def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
-             status: torch.Tensor, splits: int = 1) -> None:
+             status: torch.Tensor, splits: int = 1, glu: Optional[tuple] = None) -> None:
     """Two-SM tcgen05 product (pairs of blocks on one 256-feature tile) with a fused epilogue;
     with GEMM_SPLIT, ``splits`` slices of K as 32-bit partial sums in out [splits, M, N]."""
     M, K = a.shape
@@ -519,6 +529,12 @@ def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
     else:
         _need(tuple(out.shape) == ((M, N // 2) if mode in (GEMM_SILU_MUL, GEMM_SILU_PAIRED) else (M, N)),
               "gemm_2sm: out shape")
+    if glu is not None:
+        _need(mode in (GEMM_SILU_MUL, GEMM_SILU_PAIRED), "gemm_2sm: an activation needs a gated mode")
+        _check(lib().yalm_gemm_2sm_glu(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype), M,
+                                       N, K, mode, float(glu[0]), float(glu[1]), float(glu[2]), _p(status),
+                                       _stream()), "gemm_2sm")
+        return
     _check(lib().yalm_gemm_2sm(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype), M,
                                N, K, mode, splits, _p(status), _stream()), "gemm_2sm")
 
@@ -717,14 +733,16 @@ def gemm_grouped_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, first_r
 
 
 def glu_clamp(gu: torch.Tensor, out: torch.Tensor, n_partials: int, alpha: float, limit: float,
-              shift: float) -> None:
+              shift: float, paired: bool = False) -> None:
     """out = g' * sigmoid(alpha g') * (u' + shift), g' = min(g, limit), u' = clamp(u, +-limit)
-    (no clamps when limit <= 0); gu float32 [(n_partials,) rows, 2F] as (gate | up)."""
+    (no clamps when limit <= 0); gu float32 [(n_partials,) rows, 2F] as (gate | up) or, with
+    ``paired``, 16 gate columns then the 16 up columns of the same features, and so on."""
     rows, F = out.shape
     _need(gu.dtype == torch.float32 and gu.shape[-1] == 2 * F and gu.shape[-2] == rows
           and gu.is_contiguous() and out.is_contiguous(), "glu_clamp: shapes")
     _check(lib().yalm_glu_clamp(_p(gu), n_partials, rows * 2 * F, _p(out), dtype_code(out.dtype), rows, F,
-                                float(alpha), float(limit), float(shift), _stream()), "glu_clamp")
+                                float(alpha), float(limit), float(shift), 1 if paired else 0, _stream()),
+           "glu_clamp")
 
 
 def routed_combine(x: torch.Tensor, y: torch.Tensor, pair_row: torch.Tensor, weight: torch.Tensor,

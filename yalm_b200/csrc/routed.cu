@@ -232,29 +232,33 @@ gemm_grouped_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
   }
 }
 
-// gu [S][rows][2F] float32 (gate columns, then up columns) -> out [rows][F]; a block row per
-// matrix row (blockIdx.x), VEC features per thread (4 when F is a multiple of 4)
+// gu [S][rows][2F] float32 -> out [rows][F]; gu's columns are (gate | up) or, with `paired`,
+// groups of 16 gate columns each followed by the 16 up columns of the same features.  A block
+// row per matrix row (blockIdx.x), VEC features per thread (4 when F is a multiple of 4).
 template <typename TO, int VEC>
 __global__ void glu_clamp_kernel(const float* __restrict__ gu, int n_partials, long long partial_stride,
-                                 TO* __restrict__ out, int F, float alpha, float limit, float shift) {
+                                 TO* __restrict__ out, int F, float alpha, float limit, float shift,
+                                 int paired) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t r = blockIdx.x;
   const int f = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
   if (f >= F) return;
-  const float* p = gu + r * 2 * F + f;
+  const int gc = paired ? (f >> 4) * 32 + (f & 15) : f;          // the gate column of feature f
+  const int up_at = paired ? 16 : F;                             // its up column lies this far on
+  const float* p = gu + r * 2 * F + gc;
   float g[VEC], u[VEC];
 #pragma unroll
   for (int v = 0; v < VEC; ++v) { g[v] = 0.f; u[v] = 0.f; }
   for (int s = 0; s < n_partials; ++s) {
     const float* q = p + (size_t)s * partial_stride;
     if (VEC == 4) {
-      const float4 a = *reinterpret_cast<const float4*>(q), b = *reinterpret_cast<const float4*>(q + F);
+      const float4 a = *reinterpret_cast<const float4*>(q), b = *reinterpret_cast<const float4*>(q + up_at);
       g[0] += a.x; g[VEC > 1 ? 1 : 0] += a.y; g[VEC > 2 ? 2 : 0] += a.z; g[VEC > 3 ? 3 : 0] += a.w;
       u[0] += b.x; u[VEC > 1 ? 1 : 0] += b.y; u[VEC > 2 ? 2 : 0] += b.z; u[VEC > 3 ? 3 : 0] += b.w;
     } else {
       g[0] += q[0];
-      u[0] += q[F];
+      u[0] += q[up_at];
     }
   }
 #pragma unroll
@@ -415,7 +419,8 @@ extern "C" int yalm_gemm_grouped(const void* A, int a_dtype, const void* W, int 
 
 extern "C" int yalm_glu_clamp(const float* gu, int n_partials, long long partial_stride, void* out,
                               int out_dtype, long long rows, int F, float alpha, float limit, float shift,
-                              cudaStream_t stream) {
+                              int paired, cudaStream_t stream) {
+  if (paired && F % 16 != 0) return -2;
   if (rows <= 0 || F <= 0) return 0;
   if (rows > 0x7fffffffLL) return -4;
   const bool vec = F % 4 == 0 && partial_stride % 4 == 0 && ((uintptr_t)gu & 15) == 0;
@@ -425,9 +430,9 @@ extern "C" int yalm_glu_clamp(const float* gu, int n_partials, long long partial
 #define YALM_GC(TO)                                                                                  \
   do {                                                                                               \
     if (vec) launch_pdl(glu_clamp_kernel<TO, 4>, grid, dim3(128), 0, stream, gu, n_partials,         \
-                        partial_stride, (TO*)out, F, alpha, limit, shift);                           \
+                        partial_stride, (TO*)out, F, alpha, limit, shift, paired);                   \
     else launch_pdl(glu_clamp_kernel<TO, 1>, grid, dim3(128), 0, stream, gu, n_partials,             \
-                    partial_stride, (TO*)out, F, alpha, limit, shift);                               \
+                    partial_stride, (TO*)out, F, alpha, limit, shift, paired);                       \
   } while (0)
   if (out_dtype == DT_F32) YALM_GC(float);
   else if (out_dtype == DT_BF16) YALM_GC(__nv_bfloat16);

@@ -54,7 +54,9 @@ class ClampedGLU:
     """One gated feed-forward with clamps, y = down(g' sigmoid(slope g') (u' + shift)) with
     g' = min(gate h, limit) and u' = clamp(up h, -limit, limit): the shared expert of a routed
     feed-forward (and, with its constants, any dense feed-forward of that form).  Gate and up
-    rows are one stacked matrix; the activation sums the product's K slices as it reads them."""
+    rows are one matrix laid out as SwiGLU's, and the activation runs where SwiGLU's does: in
+    the gate/up product's epilogue, or, where that product is split over K, in the kernel that
+    sums the slices."""
 
     def __init__(self, params: dict, rt, D: int):
         self.rt = rt
@@ -64,6 +66,7 @@ class ClampedGLU:
         self.slope = float(params.get("slope", 1.0))
         self.shift = float(params.get("shift", 0.0))
         self.w_gate_up = None
+        self.paired = False
         self.w_down = None
 
     def tensor_needs(self, prefix: str = ""):
@@ -74,17 +77,21 @@ class ClampedGLU:
         parts = [gate, up]
         if any(p.dtype == torch.float32 for p in parts):
             parts = [p.to(torch.float32) for p in parts]
-        self.w_gate_up = self.rt.matrix(torch.cat(parts, 0))
+        self.paired = self.F % 16 == 0
+        if self.paired:
+            g, u = (p.reshape(self.F // 16, 16, self.D) for p in parts)
+            self.w_gate_up = self.rt.matrix(torch.stack([g, u], 1).reshape(2 * self.F, self.D))
+        else:
+            self.w_gate_up = self.rt.matrix(torch.cat(parts, 0))
         self.w_down = self.rt.matrix(down)
 
     def flops(self, n_tokens: int) -> float:
         return 2.0 * n_tokens * 3 * self.F * self.D
 
     def forward(self, h, stream, name: str) -> None:
-        from .linear import matmul_partials
-        gu, S = matmul_partials(self.rt, h, self.w_gate_up, name + "_gate_up")
         act = self.rt.buffer(name + "_act", (h.shape[0], self.F), self.rt.dtype)
-        ops.glu_clamp(gu, act, S, self.slope, self.limit, self.shift)
+        matmul_silu_mul(self.rt, h, self.w_gate_up, act, self.paired,
+                        glu=(self.slope, self.limit, self.shift))
         stream.add_linear(act, self.w_down)
 
 

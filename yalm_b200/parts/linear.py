@@ -126,11 +126,11 @@ def matmul_partials(rt, a: torch.Tensor, w: torch.Tensor, name: str) -> Tuple[to
     return buf, 1
 
 
-def _many_tokens(rt, a, w, out, mode) -> None:
+def _many_tokens(rt, a, w, out, mode, glu=None) -> None:
     """Many tokens: the two-SM kernel (pairs of blocks share a 256-feature tile, so each
     byte from L2 feeds 1.5 times the arithmetic; measured 1.03-1.31 PFLOP/s at 2,048
     tokens against 0.66-1.05 for the single-SM kernels), epilogue fused."""
-    ops.gemm_2sm(a, w, out, mode, rt.status)
+    ops.gemm_2sm(a, w, out, mode, rt.status, glu=glu)
 
 
 def matmul_store(rt, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -170,30 +170,35 @@ def matmul_into_stream(rt, a: torch.Tensor, w: torch.Tensor, stream) -> None:
 
 
 def matmul_silu_mul(rt, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
-                    paired: bool = False) -> None:
+                    paired: bool = False, glu=None) -> None:
     """out = silu(a @ Wg.T) * (a @ Wu.T).  w_gate_up is [Wg; Wu], or with ``paired``
     16 rows of Wg, the 16 rows of Wu for the same features, and so on: a 128-row
     tile of the product then holds gate and up of 64 features, and the epilogue
-    pairs them inside a warp."""
+    pairs them inside a warp.  ``glu`` = (slope, limit, shift) replaces SiLU(g) u by
+    g' sigmoid(slope g') (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit),
+    in the same epilogues."""
     M, K = a.shape
     N2 = w_gate_up.shape[0]
     if _use_tc(rt, a, w_gate_up):
         if paired:
             if M > MANY_TOKENS:
-                ops.gemm_2sm(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status)
+                ops.gemm_2sm(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status, glu=glu)
                 return
             # nearly as many tiles as SMs: one fused launch beats two slices of K plus a
             # SiLU kernel (Llama-3.2-1B sizes, 128 tiles: 3-5 % of a decode step at batch 1 to 64)
             tiles = -(-N2 // 128) * -(-M // _token_tile(M))
             if (not _small(rt, M, N2) or plan_splits(M, N2, K, rt.sm_count) == 1
                     or 5 * tiles >= 4 * rt.sm_count):
-                ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status)
+                ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status, glu=glu)
                 return
         elif not _small(rt, M, N2 // 2):
             if M > MANY_TOKENS:
-                _many_tokens(rt, a, w_gate_up, out, ops.GEMM_SILU_MUL)
+                _many_tokens(rt, a, w_gate_up, out, ops.GEMM_SILU_MUL, glu=glu)
             else:
-                ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_MUL, rt.status)
+                ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_MUL, rt.status, glu=glu)
             return
     buf, S = matmul_partials(rt, a, w_gate_up, "gate_up")
-    ops.silu_mul(buf, out, n_partials=S, paired=paired)
+    if glu is not None:
+        ops.glu_clamp(buf, out, S, glu[0], glu[1], glu[2], paired=paired)
+    else:
+        ops.silu_mul(buf, out, n_partials=S, paired=paired)
