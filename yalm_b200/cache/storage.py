@@ -53,16 +53,23 @@ class CacheNeed:
     kv_heads: int = 0
     head_dim: int = 0
     window: Optional[int] = None               # kv: keep only the last `window` positions
+    every: int = 1                             # kv: one row per `every` positions (row r: block r)
     state_shape: Tuple[int, ...] = ()          # state: per-sequence shape
     state_dtype: torch.dtype = torch.float32
 
     def group_key(self, context: int):
         if self.kind == "kv":
-            return ("kv", self.kv_heads, self.head_dim, self.capacity(context))
+            return ("kv", self.kv_heads, self.head_dim, self.capacity(context), self.every)
         return ("state", tuple(self.state_shape), self.state_dtype)
 
     def capacity(self, context: int) -> int:
+        if self.every > 1:
+            return max(1, -(-context // self.every))
         return context if self.window is None else min(context, self.window)
+
+    def rows_for(self, positions: int) -> int:
+        """Rows a sequence of ``positions`` positions needs (before the capacity's bound)."""
+        return -(-int(positions) // self.every) if self.every > 1 else int(positions)
 
 
 @dataclass
@@ -98,9 +105,14 @@ def _pool_pages(need: CacheNeed, n_slots: int, context: int, max_tokens: Optiona
     the group keeps one block per sequence instead."""
     per_slot = -(-need.capacity(context) // PAGE)
     full = n_slots * per_slot
-    if max_tokens is None or -(-int(max_tokens) // PAGE) >= full:
+    if max_tokens is None:
         return 0
-    return max(1, -(-int(max_tokens) // PAGE))
+    # one row per `every` positions: each sequence's rows are rounded up to a page of their own
+    bound = -(-int(max_tokens) // PAGE) if need.every == 1 else \
+        -(-need.rows_for(int(max_tokens)) // PAGE) + n_slots
+    if bound >= full:
+        return 0
+    return max(1, bound)
 
 
 class Cache:
@@ -232,7 +244,7 @@ class Cache:
                 continue
             want = []
             for s, n in zip(slots, lengths):
-                need = -(-min(int(n), g["capacity"]) // PAGE) - len(g["held"][s])
+                need = -(-min(g["need"].rows_for(n), g["capacity"]) // PAGE) - len(g["held"][s])
                 if need > 0:
                     want.append((s, need))
             total = sum(n for _, n in want)
@@ -251,7 +263,7 @@ class Cache:
                 g["dirty"].add(s)
         for s in slots:
             self._covered[s] = min([self.context] + [
-                len(g["held"][s]) * PAGE for g in self.groups
+                len(g["held"][s]) * PAGE * g["need"].every for g in self.groups
                 if "pool" in g and len(g["held"][s]) < g["pages_per_slot"]])
 
     def sync_tables(self) -> None:

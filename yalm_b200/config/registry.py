@@ -12,6 +12,7 @@ from typing import Any, Dict
 
 from .golulix import GolulixConfig
 from .llama import ConfigError, LlamaConfig
+from .rudazen import RudazenConfig
 
 _ARCHITECTURES: Dict[str, Any] = {}
 
@@ -50,3 +51,4 @@ def load_config(model_dir: str) -> Any:
 register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("MistralForCausalLM", LlamaConfig)
 register_architecture("Golulix", GolulixConfig)
+register_architecture("Rudazen", RudazenConfig)

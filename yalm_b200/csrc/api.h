@@ -15,8 +15,9 @@ extern "C" {
 int yalm_wait_probe(unsigned long long limit_ns, int* status, cudaStream_t stream);
 int yalm_copy_async(void* dst, const void* src, long long bytes, int to_device, cudaStream_t stream);
 int yalm_stream_wait(cudaStream_t stream);
+// x[t] = table[token t] * scale
 int yalm_embed(const int* tokens, const void* table, int table_dtype, float* x, int n_tokens,
-               int dim, int vocab, int* status, cudaStream_t stream);
+               int dim, int vocab, float scale, int* status, cudaStream_t stream);
 
 int yalm_rmsnorm(float* x, const float* partials, int n_partials, long long partial_stride,
                  const int* rows, const float* weight, void* out, int out_dtype, int n_rows,
@@ -175,6 +176,64 @@ int yalm_gemm_2sm_token_tile(int M, int N, int splits);
 // (head sizes 16, 32, 64 and 128).
 int yalm_gemm_2sm_rope(const void* A, const void* W, int ab_dtype, int M, int N, int K,
                        const yalm_rope_args* rope, int* status, cudaStream_t stream);
+
+// yalm_attention with pooled blocks beside a sliding window (window > 0): pool_k / pool_v hold one
+// (mean key, mean value) row per block of `pool` positions, [slots][G][pool_capacity][hd] or pages
+// named by pool_table; a query at position p sees block b if b * pool + pool - 1 <= p - window, in
+// the same softmax as the window's keys.
+int yalm_attention_pooled(const void* q, const void* kv_step, const void* k_cache, const void* v_cache,
+                          const int* token_seq, const int* q_start, const int* seq_slot,
+                          const int* slot_pos, void* out, float* part_o, float* part_ml, int dtype,
+                          int n_tokens, int H, int G, int hd, int capacity, int window, float scale,
+                          int nsplit, const int* page_table, int pages_per_slot, int n_pages,
+                          const void* pool_k, const void* pool_v, int pool, int pool_capacity,
+                          const int* pool_table, int pool_pps, int pool_pages, cudaStream_t stream);
+
+// ---- qk_store.cu: after a q/k(/v) product with whole-projection norms and partial rotation ----
+// qkv: float32 slices [n_partials][tokens][(H + G (+ G)) hd] = (q | k | v, v only with has_v).
+// q_norm [H hd] / k_norm [G hd] (null: no norm): q <- q / sqrt(sum q^2 / n_q + eps) * q_norm over
+// the whole row, likewise k.  The first `dims` features of every head are rotated by
+// pos * freq[i] (freq [dims / 2]), pairs (i, i + dims/2), or (2i, 2i+1) with `neighbours`; cos and
+// sin are multiplied by `mult`.  Values: the v rows, or without them the keys as projected.
+int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long long partial_stride,
+                            const float* q_norm, const float* k_norm, int n_q, int n_k, float eps,
+                            const float* freq, int dims, int neighbours, float mult,
+                            const int* token_seq, const int* q_start, const int* seq_slot,
+                            const int* slot_pos, void* q_out, void* kv_step, void* k_cache,
+                            void* v_cache, int dtype, int n_tokens, int H, int G, int hd, int has_v,
+                            int capacity, int write_cache, const int* page_table, int pages_per_slot,
+                            int n_pages, cudaStream_t stream);
+// The mean key and mean value of every block of `pool` positions that this step completes, into
+// the pooled cache's row of that block; positions of this step come from kv_step, earlier ones
+// from the ring (capacity >= pool - 1), before the step's late ring write if there is one.
+int yalm_pool_blocks(const void* kv_step, const void* k_cache, const void* v_cache, const int* q_start,
+                     const int* seq_slot, const int* slot_pos, void* pool_k, void* pool_v, int dtype,
+                     int n_seqs, int max_q_len, int G, int hd, int capacity, int pool,
+                     const int* page_table, int pages_per_slot, int n_pages, int pool_capacity,
+                     const int* pool_table, int pool_pps, int pool_pages, int* status,
+                     cudaStream_t stream);
+
+// ---- sum_norm.cu: layers that norm after the residual sum ---------------------------------
+// x [rows, dim] <- n(alpha x + scale0 B0 + scale1 B1, weight), n(v, w) = v / sqrt(mean v^2 + eps) w;
+// Bj is the sum of nj float32 slices (sj floats apart), itself normed with wj and branch_eps when
+// wj is not null.  h (null, or [rows, dim] of h_dtype) receives the new x in that type too.
+int yalm_sum_norm(float* x, float alpha, int n_branches, const float* p0, int n0, long long s0,
+                  const float* w0, float scale0, const float* p1, int n1, long long s1,
+                  const float* w1, float scale1, float branch_eps, const float* weight, float eps,
+                  void* h, int h_dtype, int rows, int dim, cudaStream_t stream);
+int yalm_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream);
+// out [rows, heads * size] = each head's `size` values of o (float32) normed with w [size]
+int yalm_head_norm(const float* o, const float* w, void* out, int out_dtype, long long rows, int heads,
+                   int size, float eps, cudaStream_t stream);
+
+// ---- recurrence.cu: S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t per head ------
+// proj: float32 slices [n_partials][tokens][2 H dk + H dv] = (q | f | v) before activation:
+// q = silu(.), f = lower + (1 - lower) sigmoid(. + f_bias); state [slots][H][dk][dv] float32;
+// out float32 [tokens][H dv]
+int yalm_gated_recurrence(const float* proj, int n_partials, long long partial_stride,
+                          const float* f_bias, const float* lower, const int* q_start,
+                          const int* seq_slot, float* state, float* out, int n_seqs, int H, int dk,
+                          int dv, cudaStream_t stream);
 
 // ---- small_ops.cu ---------------------------------------------------------------------
 // x[t] = E[token t] + P[row t] (also into x_copy when given): row = buckets for a sequence's

@@ -83,6 +83,23 @@ template <> struct Vec8<float> {
   static __device__ __forceinline__ void load(const float* p, float* f) { unpack(load_raw(p), f); }
 };
 
+// Pooled blocks beside a sliding window: one (mean key, mean value) row for every block of
+// `pool` positions, in a cache of its own with one row per block ([slots][G][capacity][hd], or
+// pages with a table, like the keys').  A query at position pos sees, beside its window, the
+// blocks that lie wholly before it: block b if b * pool + pool - 1 <= pos - window.  The rows
+// take part in the same softmax as the window's keys.  pool == 0: none.
+struct PoolArgs {
+  const void* k;
+  const void* v;
+  const int* table;
+  int pps, n_pages, capacity, pool;
+};
+__host__ __device__ __forceinline__ int pooled_visible(int pos, int window, int pool) {
+  if (pool <= 0 || window <= 0) return 0;
+  const int n = pos - window + 1;
+  return n > 0 ? n / pool : 0;
+}
+
 // LPK lanes share one key (LPK*8 >= hd); a warp handles 32/LPK keys at a time.
 template <typename T, int LPK>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
@@ -92,7 +109,7 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
                   const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
                   T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                   int H, int G, int hd, int capacity, int window, int nsplit, float scale, int t0,
-                  const int* __restrict__ page_table, int pps, int n_pages) {
+                  const int* __restrict__ page_table, int pps, int n_pages, PoolArgs pl) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int KPW = 32 / LPK;                 // keys per warp per iteration
@@ -116,10 +133,14 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
   const int qs = q_start[b];
   const int pos = past + (t - qs);
   const int lo = first_visible(pos, window);
-  const int nkeys = pos - lo + 1;
+  // the keys in one numbering: the visible pooled blocks first, then the positions lo .. pos
+  const int nb = pooled_visible(pos, window, pl.pool);
+  const int nkeys = nb + pos - lo + 1;
   const int per = (nkeys + nsplit - 1) / nsplit;
-  const int s_lo = lo + split * per;
-  const int s_hi = min(lo + (split + 1) * per, pos + 1);
+  const int s_lo = split * per;
+  const int s_hi = min((split + 1) * per, nkeys);
+  const T* pool_k = reinterpret_cast<const T*>(pl.k);
+  const T* pool_v = reinterpret_cast<const T*>(pl.v);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane % LPK, kg = lane / LPK;
@@ -154,11 +175,16 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
     bool valid[ATT_U];
 #pragma unroll
     for (int u = 0; u < ATT_U; ++u) {
-      const int key = base + u * GROUPS + kg;
-      valid[u] = key < s_hi;
+      const int idx = base + u * GROUPS + kg;
+      const int key = lo + idx - nb;
+      valid[u] = idx < s_hi;
       if (valid[u] && lane_on) {
         const T *kp, *vp;
-        if (key >= past) {
+        if (idx < nb) {
+          const size_t row = kv_row_offset(pl.table, pl.pps, pl.n_pages, slot, g, G, pl.capacity, idx, hd) + e0;
+          kp = pool_k + row;
+          vp = pool_v + row;
+        } else if (key >= past) {
           kp = kv_step + (size_t)(qs + key - past) * step_row + (size_t)g * hd + e0;
           vp = kp + (size_t)G * hd;
         } else {
@@ -550,7 +576,7 @@ static int launch_attention(const void* q, const void* kv_step, const void* k_ca
                             const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                             float* part_ml, int n_tokens, int H, int G, int hd, int capacity,
                             int window, float scale_in, int nsplit, const int* page_table, int pps,
-                            int n_pages, cudaStream_t stream) {
+                            int n_pages, PoolArgs pl, cudaStream_t stream) {
   const int R = H / G;
   const int nchunks = (R + ATT_RT - 1) / ATT_RT;
   const dim3 block(ATT_WARPS * 32);
@@ -562,7 +588,7 @@ static int launch_attention(const void* q, const void* kv_step, const void* k_ca
   launch_pdl(attn_token_kernel<T, LPK>, dim3(grid), dim3(block), 0, stream,                                         \
       (const T*)q, (const T*)kv_step, (const T*)k_cache, (const T*)v_cache, token_seq, q_start, \
       seq_slot, slot_pos, (T*)out, part_o, part_ml, H, G, hd, capacity, window, nsplit, scale, t0, \
-      page_table, pps, n_pages)
+      page_table, pps, n_pages, pl)
   if (hd <= 16) YALM_ATT_CASE(2);
   else if (hd <= 32) YALM_ATT_CASE(4);
   else if (hd <= 64) YALM_ATT_CASE(8);
@@ -586,13 +612,13 @@ using namespace yalm;
 
 // part_o: [n_tokens, H, nsplit, hd] floats, part_ml: [n_tokens, H, nsplit, 2]
 // floats; both are needed only when nsplit > 1.
-extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_cache,
-                              const void* v_cache, const int* token_seq, const int* q_start,
-                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
-                              float* part_ml, int dtype, int n_tokens, int H, int G, int hd,
-                              int capacity, int window, float scale, int nsplit,
-                              const int* page_table, int pages_per_slot, int n_pages,
-                              cudaStream_t stream) {
+static int attention_any(const void* q, const void* kv_step, const void* k_cache,
+                         const void* v_cache, const int* token_seq, const int* q_start,
+                         const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                         float* part_ml, int dtype, int n_tokens, int H, int G, int hd,
+                         int capacity, int window, float scale, int nsplit,
+                         const int* page_table, int pages_per_slot, int n_pages, PoolArgs pl,
+                         cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd % 8 != 0 || hd > 256 || hd <= 0) return -2;     // head sizes: multiples of 8 up to 256
   if (G <= 0 || H % G != 0) return -3;
@@ -601,16 +627,47 @@ extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_
   if (dtype == DT_F32)
     return launch_attention<float>(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot,
                                    slot_pos, out, part_o, part_ml, n_tokens, H, G, hd, capacity,
-                                   window, scale, nsplit, page_table, pages_per_slot, n_pages, stream);
+                                   window, scale, nsplit, page_table, pages_per_slot, n_pages, pl, stream);
   if (dtype == DT_F16)
     return launch_attention<__half>(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot,
                                     slot_pos, out, part_o, part_ml, n_tokens, H, G, hd, capacity,
-                                    window, scale, nsplit, page_table, pages_per_slot, n_pages, stream);
+                                    window, scale, nsplit, page_table, pages_per_slot, n_pages, pl, stream);
   if (dtype != DT_BF16) return -3;
   return launch_attention<__nv_bfloat16>(q, kv_step, k_cache, v_cache, token_seq, q_start,
                                          seq_slot, slot_pos, out, part_o, part_ml, n_tokens, H, G,
                                          hd, capacity, window, scale, nsplit, page_table, pages_per_slot, n_pages,
-                                         stream);
+                                         pl, stream);
+}
+
+extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_cache,
+                              const void* v_cache, const int* token_seq, const int* q_start,
+                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                              float* part_ml, int dtype, int n_tokens, int H, int G, int hd,
+                              int capacity, int window, float scale, int nsplit,
+                              const int* page_table, int pages_per_slot, int n_pages,
+                              cudaStream_t stream) {
+  const PoolArgs none = {nullptr, nullptr, nullptr, 0, 0, 0, 0};
+  return attention_any(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot, slot_pos, out,
+                       part_o, part_ml, dtype, n_tokens, H, G, hd, capacity, window, scale, nsplit,
+                       page_table, pages_per_slot, n_pages, none, stream);
+}
+
+// yalm_attention with pooled blocks beside the window (window > 0): pool_k / pool_v hold one row
+// per block of `pool` positions, [slots][G][pool_capacity][hd] or pages named by pool_table.
+extern "C" int yalm_attention_pooled(const void* q, const void* kv_step, const void* k_cache,
+                                     const void* v_cache, const int* token_seq, const int* q_start,
+                                     const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                                     float* part_ml, int dtype, int n_tokens, int H, int G, int hd,
+                                     int capacity, int window, float scale, int nsplit,
+                                     const int* page_table, int pages_per_slot, int n_pages,
+                                     const void* pool_k, const void* pool_v, int pool, int pool_capacity,
+                                     const int* pool_table, int pool_pps, int pool_pages,
+                                     cudaStream_t stream) {
+  if (pool <= 0 || window <= 0 || pool_capacity <= 0) return -2;
+  const PoolArgs pl = {pool_k, pool_v, pool_table, pool_pps, pool_pages, pool_capacity, pool};
+  return attention_any(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot, slot_pos, out,
+                       part_o, part_ml, dtype, n_tokens, H, G, hd, capacity, window, scale, nsplit,
+                       page_table, pages_per_slot, n_pages, pl, stream);
 }
 
 // Decode attention (see attn_decode_kernel).  Every query is the newest token of

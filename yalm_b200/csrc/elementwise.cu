@@ -19,7 +19,7 @@ int g_pdl_enabled = 1;
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                             float* __restrict__ x, int dim, int vocab, int* status) {
+                             float* __restrict__ x, int dim, int vocab, float scale, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -30,7 +30,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
   }
   const T* row = table + (size_t)tok * dim;
   float* out = x + (size_t)t * dim;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = to_float(row[i]) * scale;   // * 1 is exact
 }
 
 // ------------------------------------------------------------------ rmsnorm
@@ -487,18 +487,18 @@ extern "C" int yalm_copy_async(void* dst, const void* src, long long bytes, int 
 extern "C" int yalm_stream_wait(cudaStream_t stream) { return (int)cudaStreamSynchronize(stream); }
 
 extern "C" int yalm_embed(const int* tokens, const void* table, int table_dtype, float* x,
-                          int n_tokens, int dim, int vocab, int* status, cudaStream_t stream) {
+                          int n_tokens, int dim, int vocab, float scale, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const int threads = dim >= 1024 ? 256 : 128;
   if (table_dtype == DT_F32)
     launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, x, dim,
-                                                          vocab, status);
+                                                          vocab, scale, status);
   else if (table_dtype == DT_BF16)
     launch_pdl(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream,
-               tokens, (const __nv_bfloat16*)table, x, dim, vocab, status);
+               tokens, (const __nv_bfloat16*)table, x, dim, vocab, scale, status);
   else if (table_dtype == DT_F16)
     launch_pdl(embed_kernel<__half>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
-               (const __half*)table, x, dim, vocab, status);
+               (const __half*)table, x, dim, vocab, scale, status);
   else
     return -3;
   YALM_LAUNCH_CHECK();

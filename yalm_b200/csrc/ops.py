@@ -47,7 +47,7 @@ def dtype_code(dt: torch.dtype) -> int:
 _c = ctypes
 _vp, _i, _ll, _f, _ull = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_float, _c.c_ulonglong
 _SIGNATURES = {
-    "yalm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp],
+    "yalm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp, _vp],
     "yalm_rmsnorm": [_vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "yalm_copy_async": [_vp, _vp, _ll, _i, _vp],
     "yalm_wait_probe": [_ull, _vp, _vp],
@@ -93,6 +93,17 @@ _SIGNATURES = {
     "yalm_gemm_grouped_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _f, _f,
                              _f, _vp, _vp],
     "yalm_routed_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "yalm_attention_pooled": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                              _i, _i, _f, _i, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
+    "yalm_qk_norm_rope_store": [_vp, _i, _ll, _vp, _vp, _i, _i, _f, _vp, _i, _i, _f, _vp, _vp, _vp, _vp,
+                                _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
+    "yalm_pool_blocks": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i,
+                         _i, _vp, _i, _i, _vp, _vp],
+    "yalm_sum_norm": [_vp, _f, _i, _vp, _i, _ll, _vp, _f, _vp, _i, _ll, _vp, _f, _f, _vp, _f, _vp, _i, _i,
+                      _i, _vp],
+    "yalm_cast_rows": [_vp, _vp, _i, _ll, _vp],
+    "yalm_head_norm": [_vp, _vp, _vp, _i, _ll, _i, _i, _f, _vp],
+    "yalm_gated_recurrence": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
 }
 
 _lib = None
@@ -182,13 +193,15 @@ def _pages(pages, cache: torch.Tensor, G: int, hd: int):
 
 
 # --------------------------------------------------------------------------
-def embed(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:
+def embed(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor, status: torch.Tensor,
+          scale: float = 1.0) -> None:
+    """x[t] = table[tokens[t]] * scale, float32."""
     n, dim = x.shape
     _need(tokens.dtype == torch.int32 and tokens.numel() >= n, "embed: tokens must be int32 [n]")
     _need(table.shape[1] == dim and x.dtype == torch.float32 and x.is_contiguous()
           and table.is_contiguous(), "embed: shapes")
     _check(lib().yalm_embed(_p(tokens), _p(table), dtype_code(table.dtype), _p(x), n, dim,
-                            table.shape[0], _p(status), _stream()), "embed")
+                            table.shape[0], float(scale), _p(status), _stream()), "embed")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
@@ -285,7 +298,11 @@ def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_c
               batch, slot_pos: torch.Tensor, out: torch.Tensor, H: int, G: int, hd: int,
               capacity: int, window: Optional[int], nsplit: int = 1,
               part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-              pages=None, chunk: Optional[int] = None, scale: Optional[float] = None) -> None:
+              pages=None, chunk: Optional[int] = None, scale: Optional[float] = None,
+              pooled=None) -> None:
+    """``pooled`` = (pool_k, pool_v, pool, pool_capacity, pool_pages): one (mean key, mean value)
+    row per block of ``pool`` positions, seen beside the window by the queries it lies wholly
+    before (see ``pool_blocks``)."""
     n = q.shape[0]
     pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype,
@@ -297,6 +314,19 @@ def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_c
               and part_o.numel() >= n * H * nsplit * hd and part_ml.numel() >= n * H * nsplit * 2
               and part_o.dtype == torch.float32 and part_ml.dtype == torch.float32,
               "attention: split scratch")
+    if pooled is not None:
+        pool_k, pool_v, pool, pool_cap, pool_pages = pooled
+        _need(window and not chunk and pool > 0, "attention: pooled blocks go with a sliding window")
+        _need(pool_k.dtype == pool_v.dtype == q.dtype and pool_k.is_contiguous() and pool_v.is_contiguous(),
+              "attention: pooled rows in the keys' type")
+        ppt, ppps, pnpg = _pages(pool_pages, pool_k, G, hd)
+        _check(lib().yalm_attention_pooled(
+            _p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.token_seq), _p(batch.q_start),
+            _p(batch.seq_slot), _p(slot_pos), _p(out), _p(part_o), _p(part_ml), dtype_code(q.dtype), n, H,
+            G, hd, capacity, int(window), float(scale or 0.0), nsplit, pt, pps, npg, _p(pool_k),
+            _p(pool_v), int(pool), int(pool_cap), ppt, ppps, pnpg, _stream()), "attention (pooled)",
+            kernels=2 if nsplit > 1 else 1)
+        return
     _check(lib().yalm_attention(_p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.token_seq),
                                 _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos), _p(out),
                                 _p(part_o), _p(part_ml), dtype_code(q.dtype), n, H, G, hd,
@@ -642,6 +672,116 @@ def residual_add(x: torch.Tensor, y: torch.Tensor, partials: Optional[torch.Tens
               and partials.numel() >= n_partials * x.numel(), "residual_add: partials")
     _check(lib().yalm_residual_add(_p(x), _p(y), _p(partials) if n_partials else None, n_partials,
                                    x.numel(), x.numel(), _stream()), "residual_add")
+
+
+# ---- whole-projection norms, partial rotation, pooled blocks ----------------------------
+def qk_norm_rope_store(qkv: torch.Tensor, n_partials: int, q_norm: Optional[torch.Tensor],
+                       k_norm: Optional[torch.Tensor], n_q: int, n_k: int, eps: float,
+                       freq: torch.Tensor, dims: int, neighbours: bool, mult: float, batch,
+                       q_out: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
+                       v_cache: torch.Tensor, slot_pos: torch.Tensor, H: int, G: int, hd: int,
+                       has_v: bool, capacity: int, write_cache: bool = True, pages=None) -> None:
+    """qkv float32 [(s,) N, (H + G (+ G)) hd] -> q_out [N, H hd], kv_step [N, 2, G, hd] and the cache
+    rows: q and k normed over their whole rows (n_q, n_k true features), the first ``dims``
+    features of each head rotated (pairs (i, i + dims/2), or (2i, 2i+1) with ``neighbours``), cos
+    and sin times ``mult``; values are the v rows or, without them, the keys as projected."""
+    n = q_out.shape[0]
+    row = (H + (2 if has_v else 1) * G) * hd
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
+    _need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[-1] == row
+          and qkv.shape[-2] == n, "qk_norm_rope_store: qkv float32 [(s,) N, row]")
+    for w, size in ((q_norm, H * hd), (k_norm, G * hd)):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == size and w.is_contiguous()),
+              "qk_norm_rope_store: norm weights float32 [heads * hd]")
+    _need(freq.dtype == torch.float32 and freq.numel() >= max(1, dims // 2) and dims % 2 == 0
+          and 0 <= dims <= hd, "qk_norm_rope_store: freq float32 [dims / 2]")
+    _need(q_out.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype and q_out.is_contiguous()
+          and kv_step.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous(),
+          "qk_norm_rope_store: outputs of one type, contiguous")
+    _check(lib().yalm_qk_norm_rope_store(
+        _p(qkv), n_partials, n * row, _p(q_norm), _p(k_norm), int(n_q), int(n_k), float(eps), _p(freq),
+        int(dims), 1 if neighbours else 0, float(mult), _p(batch.token_seq), _p(batch.q_start),
+        _p(batch.seq_slot), _p(slot_pos), _p(q_out), _p(kv_step), _p(k_cache), _p(v_cache),
+        dtype_code(q_out.dtype), n, H, G, hd, 1 if has_v else 0, capacity, 1 if write_cache else 0, pt,
+        pps, npg, _stream()), "qk_norm_rope_store")
+
+
+def pool_blocks(kv_step: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch,
+                slot_pos: torch.Tensor, pool_k: torch.Tensor, pool_v: torch.Tensor, G: int, hd: int,
+                capacity: int, pool: int, pool_capacity: int, status: torch.Tensor, pages=None,
+                pool_pages=None) -> None:
+    """Mean key and mean value of every block of ``pool`` positions that this step completes,
+    into row ``block`` of the pooled cache."""
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
+    ppt, ppps, pnpg = _pages(pool_pages, pool_k, G, hd)
+    _need(kv_step.dtype == k_cache.dtype == v_cache.dtype == pool_k.dtype == pool_v.dtype
+          and kv_step.is_contiguous() and pool_k.is_contiguous() and pool_v.is_contiguous(),
+          "pool_blocks: one type, contiguous")
+    _check(lib().yalm_pool_blocks(_p(kv_step), _p(k_cache), _p(v_cache), _p(batch.q_start),
+                                  _p(batch.seq_slot), _p(slot_pos), _p(pool_k), _p(pool_v),
+                                  dtype_code(kv_step.dtype), batch.n_seqs, max(batch.q_lens), G, hd,
+                                  capacity, int(pool), pt, pps, npg, int(pool_capacity), ppt, ppps, pnpg,
+                                  _p(status), _stream()), "pool_blocks")
+
+
+# ---- layers that norm after the residual sum ------------------------------------------------
+def sum_norm(x: torch.Tensor, alpha: float, branches, weight: torch.Tensor, eps: float,
+             h: Optional[torch.Tensor] = None, branch_eps: float = 0.0) -> None:
+    """x <- n(alpha x + sum_b scale_b B_b, weight) in place (float32), and into ``h`` in h's type.
+    ``branches``: up to two (slices float32 [S, N, dim], S, norm weight or None, scale); a branch
+    with a weight is itself normed over the row (with ``branch_eps``) before it is added."""
+    n, dim = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and weight.dtype == torch.float32
+          and weight.numel() == dim, "sum_norm: x float32 [N, dim], weight float32 [dim]")
+    _need(len(branches) <= 2, "sum_norm: at most two branches")
+    _need(h is None or (h.is_contiguous() and tuple(h.shape) == (n, dim)), "sum_norm: h like x")
+    args = []
+    for buf, S, w, scale in branches:
+        _need(buf.dtype == torch.float32 and buf.is_contiguous() and buf.numel() >= S * n * dim,
+              "sum_norm: a branch is float32 [S, N, dim]")
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == dim), "sum_norm: branch weight")
+        args += [_p(buf), int(S), n * dim, _p(w), float(scale)]
+    while len(args) < 10:
+        args += [None, 0, 0, None, 0.0]
+    _check(lib().yalm_sum_norm(_p(x), float(alpha), len(branches), *args, float(branch_eps), _p(weight),
+                               float(eps), _p(h), dtype_code(h.dtype) if h is not None else F32, n, dim,
+                               _stream()), "sum_norm")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+          and out.numel() == x.numel(), "cast_rows: float32 in, same size out")
+    _check(lib().yalm_cast_rows(_p(x), _p(out), dtype_code(out.dtype), x.numel(), _stream()), "cast_rows")
+
+
+def head_norm(o: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, size: int,
+              eps: float) -> None:
+    """out [N, heads * size] = every head's values of o (float32) normed over ``size`` with weight."""
+    n = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.shape[1] == heads * size
+          and weight.dtype == torch.float32 and weight.numel() == size and out.is_contiguous()
+          and tuple(out.shape) == (n, heads * size), "head_norm: shapes")
+    _check(lib().yalm_head_norm(_p(o), _p(weight), _p(out), dtype_code(out.dtype), n, heads, size,
+                                float(eps), _stream()), "head_norm")
+
+
+def gated_recurrence(proj: torch.Tensor, n_partials: int, f_bias: torch.Tensor, lower: torch.Tensor,
+                     batch, state: torch.Tensor, out: torch.Tensor, H: int, dk: int, dv: int) -> None:
+    """S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t per head over a step's tokens, from
+    the fused projection (q | f | v) as float32 slices [(s,) N, 2 H dk + H dv]; ``state`` float32
+    [slots, H, dk, dv] is read at the step's start and written at its end; out float32 [N, H dv]."""
+    n = out.shape[0]
+    row = 2 * H * dk + H * dv
+    _need(proj.dtype == torch.float32 and proj.is_contiguous() and proj.shape[-1] == row
+          and proj.shape[-2] == n, "gated_recurrence: projection float32 [(s,) N, 2 H dk + H dv]")
+    _need(f_bias.dtype == lower.dtype == torch.float32 and f_bias.numel() == lower.numel() == H * dk,
+          "gated_recurrence: bias and lower bound float32 [H dk]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv)
+          and out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == H * dv,
+          "gated_recurrence: state float32 [slots, H, dk, dv], out float32 [N, H dv]")
+    _check(lib().yalm_gated_recurrence(_p(proj), n_partials, n * row, _p(f_bias), _p(lower),
+                                       _p(batch.q_start), _p(batch.seq_slot), _p(state), _p(out),
+                                       batch.n_seqs, H, dk, dv, _stream()), "gated_recurrence")
 
 
 # ---- a routed feed-forward --------------------------------------------------------------

@@ -18,7 +18,24 @@ Options beyond that, each a parameter (all off for the Llama / Mistral decoder):
   head size, so the smaller of the two is padded with zero rows of the weights (zero
   columns of Wo): scores and outputs are unchanged, and nothing is padded when they agree.
   Only an encoding without rotation allows it (rotation pairs depend on the head size);
-* ``head_gate``: head h's output is multiplied by sigmoid(Wg h)_h, Wg [H, width], before Wo.
+* ``head_gate``: head h's output is multiplied by sigmoid(Wg h)_h, Wg [H, width], before Wo;
+* ``element_gate``: the concatenated heads are multiplied feature by feature by sigmoid(Wg h),
+  Wg [H * value size, width], before Wo;
+* ``qk_norm`` = {"eps": e}: q and k are each normed over the WHOLE projection (all heads of a
+  token at once) with weights ``q.norm`` / ``k.norm`` of that size, before rotation (needs the
+  ``rope_partial`` position encoding, whose kernel does both);
+* ``head_temp``: head h's scores are multiplied by ``temp``[h]; the factor is folded into head
+  h's part of the ``q.norm`` weight in 32 bits when the weights are bound;
+* ``values_from_keys``: there is no v projection; a position's value is its key as projected,
+  before norm and rotation;
+* ``pool`` = P (with a window W): beside the last W positions a query sees one (mean key, mean
+  value) for every block of P positions that lies wholly before its window (block b if
+  b P + P - 1 <= pos - W), in the same softmax.  The means are formed from the rows as the
+  cache holds them when a block completes, and live in a second cache with one row per block;
+  the ring of the window keeps max(W, P) rows so that a completing block's rows are still there;
+* ``exact_softmax``: scores, softmax weights and the weighted sum of values in 32-bit arithmetic
+  (the FMA attention kernels on the 16-bit cache) instead of the tensor-core kernels, whose
+  weights are rounded to 16 bits.
 """
 from __future__ import annotations
 
@@ -47,6 +64,22 @@ class GQAAttention:
         self.chunk: Optional[int] = params.get("chunk") or None
         self.scale: Optional[float] = params.get("scale") or None
         self.head_gate = bool(params.get("head_gate", False))
+        self.element_gate = bool(params.get("element_gate", False))
+        self.qk_norm = params.get("qk_norm") or None
+        self.head_temp = bool(params.get("head_temp", False))
+        self.values_from_keys = bool(params.get("values_from_keys", False))
+        self.pool: Optional[int] = params.get("pool") or None
+        self.exact = bool(params.get("exact_softmax", False))
+        if self.head_gate and self.element_gate:
+            raise ValueError("a gate per head and a gate per feature exclude each other")
+        if self.pool and not self.window:
+            raise ValueError("pooled blocks lie before a sliding window: the mixer needs one")
+        if self.values_from_keys and self.hd_v != self.hd_k:
+            raise ValueError(f"values that are the keys have the keys' size {self.hd_k}, not {self.hd_v}")
+        if (self.qk_norm or self.values_from_keys) and params["position"].kind != "rope_partial":
+            raise ValueError("whole-projection norms and values from keys need the rope_partial encoding")
+        if self.head_temp and not self.qk_norm:
+            raise ValueError("a factor per head is folded into the q norm's weight: the mixer needs qk_norm")
         if self.window and self.chunk:
             raise ValueError("a sliding window and a chunked mask exclude each other")
         if self.H % self.G:
@@ -55,7 +88,7 @@ class GQAAttention:
         # the one head size the kernels run with
         self.hd = max(self.hd_k, self.hd_v)
         if self.hd_k != self.hd_v or self.hd % 8:
-            if position.kind != "none":
+            if position.kind not in ("none", "rope_partial"):
                 raise ValueError(f"head sizes {self.hd_k} (keys) and {self.hd_v} (values) need padding "
                                  f"to one multiple of 8, which a rotating position encoding rules out")
             self.hd = -(-self.hd // 16) * 16
@@ -65,7 +98,12 @@ class GQAAttention:
             raise ValueError(f"head size {self.hd} is not supported by the attention kernel "
                              f"(up to 256)")
         self.span = self.window or self.chunk          # the most keys a query sees, if bounded
+        if position.kind == "rope_partial" and int(position.params.get("head_dim", self.hd)) != self.hd:
+            position = type(position)(position.kind, {**position.params, "head_dim": self.hd},
+                                      position.tensors)
         self.position = make_part(POSITIONS, position, rt)
+        self.q_norm = self.k_norm = None
+        self._store_extras = {}
         self.w_qkv = None
         self.w_o = None
         self.w_g = None
@@ -75,9 +113,27 @@ class GQAAttention:
                  "k": TensorNeed((self.G * self.hd_k, self.D)),
                  "v": TensorNeed((self.G * self.hd_v, self.D)),
                  "o": TensorNeed((self.D, self.H * self.hd_v))}
+        if self.values_from_keys:
+            del needs["v"]
         if self.head_gate:
             needs["g"] = TensorNeed((self.H, self.D))
+        if self.element_gate:
+            needs["g"] = TensorNeed((self.H * self.hd_v, self.D))
+        if self.qk_norm:
+            needs["q.norm"] = TensorNeed((self.H * self.hd_k,), init="ones")
+            needs["k.norm"] = TensorNeed((self.G * self.hd_k,), init="ones")
+        if self.head_temp:
+            needs["temp"] = TensorNeed((self.H,), init="ones")
         return needs
+
+    def _pad_vector(self, w: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+        """float32 [heads * size] -> [heads * hd] with zeros after each head's own."""
+        w = self.rt.vector(w)
+        if size == self.hd:
+            return w
+        out = torch.zeros((heads, self.hd), dtype=torch.float32, device=w.device)
+        out[:, :size] = w.view(heads, size)
+        return out.view(-1).contiguous()
 
     def _pad_heads(self, w: torch.Tensor, heads: int, size: int) -> torch.Tensor:
         """[heads * size, D] -> [heads * hd, D] with zero rows after each head's own."""
@@ -89,8 +145,9 @@ class GQAAttention:
 
     def bind(self, tensors) -> None:
         parts = [self._pad_heads(tensors["q"], self.H, self.hd_k),
-                 self._pad_heads(tensors["k"], self.G, self.hd_k),
-                 self._pad_heads(tensors["v"], self.G, self.hd_v)]
+                 self._pad_heads(tensors["k"], self.G, self.hd_k)]
+        if not self.values_from_keys:
+            parts.append(self._pad_heads(tensors["v"], self.G, self.hd_v))
         if any(p.dtype == torch.float32 for p in parts):
             parts = [p.to(torch.float32) for p in parts]
         self.w_qkv = self.rt.matrix(torch.cat(parts, 0))
@@ -102,9 +159,25 @@ class GQAAttention:
         self.w_o = self.rt.matrix(w_o)
         if self.head_gate:
             self.w_g = self.rt.matrix(tensors["g"])
+        if self.element_gate:
+            self.w_g = self.rt.matrix(self._pad_heads(tensors["g"], self.H, self.hd_v))
+        if self.qk_norm:
+            self.q_norm = self._pad_vector(tensors["q.norm"], self.H, self.hd_k)
+            self.k_norm = self._pad_vector(tensors["k.norm"], self.G, self.hd_k)
+            if self.head_temp:
+                temp = self.rt.vector(tensors["temp"])
+                self.q_norm = (self.q_norm.view(self.H, self.hd) * temp[:, None]).reshape(-1).contiguous()
+            self._store_extras["norms"] = (self.q_norm, self.k_norm, self.H * self.hd_k,
+                                           self.G * self.hd_k, float(self.qk_norm["eps"]))
+        if self.values_from_keys:
+            self._store_extras["has_v"] = False
 
-    def cache_need(self) -> CacheNeed:
-        return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=self.span)
+    def cache_need(self):
+        if not self.pool:
+            return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=self.span)
+        # the ring keeps a completing block's rows; the pooled rows are never dropped
+        return {"kv": CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=max(self.window, self.pool)),
+                "pool": CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=None, every=self.pool)}
 
     def decode_chunk(self, batch) -> int:
         """Keys per block of the decode kernel: 64 KiB of keys and values, so
@@ -173,14 +246,18 @@ class GQAAttention:
             seen = sum((c - 1) % self.chunk + 1 for c in contexts if c > 0)
         else:
             seen = sum(min(c, self.window) if self.window else c for c in contexts)
+        if self.pool:
+            seen += sum(max(0, c - self.window) // self.pool for c in contexts)
         return seen * 2 * self.G * self.hd * element_size
 
     def flops(self, q_lens, past) -> float:
         """Multiply-adds times two of a step: the four projections and, for each query,
         scores and value mix over the keys it sees."""
         n = sum(q_lens)
-        linear = 2.0 * n * ((self.H + 2 * self.G) * self.hd * self.D + self.D * self.H * self.hd
-                            + (self.H * self.D if self.head_gate else 0))
+        kv = 1 if self.values_from_keys else 2
+        linear = 2.0 * n * ((self.H + kv * self.G) * self.hd * self.D + self.D * self.H * self.hd
+                            + (self.H * self.D if self.head_gate else 0)
+                            + (self.H * self.hd * self.D if self.element_gate else 0))
         pairs = 0
         for q, p in zip(q_lens, past):
             for pos in range(p, p + q):
@@ -188,11 +265,17 @@ class GQAAttention:
                     pairs += pos % self.chunk + 1
                 else:
                     pairs += min(pos + 1, self.window) if self.window else pos + 1
+                    if self.pool:
+                        pairs += max(0, pos - self.window + 1) // self.pool
         return linear + 4.0 * self.H * self.hd * pairs
 
     def forward(self, h, batch, stream, view, shared: bool = False):
         rt, H, G, hd = self.rt, self.H, self.G, self.hd
         n = batch.n_tokens
+        pool_view = None
+        if isinstance(view, dict):
+            pool_view, view = view["pool"], view["kv"]
+        extras = self._store_extras
         q = rt.buffer("q_rot", (n, H * hd), rt.dtype)
         # many tokens: the q/k/v product rotates and stores in its own epilogue
         table = getattr(self.position, "step_table", None)
@@ -200,11 +283,12 @@ class GQAAttention:
                  and ops.gemm_2sm_rope_usable(h, self.w_qkv, hd))
         if not fused:
             qkv, S = matmul_partials(rt, h, self.w_qkv, "qkv")
-        if self.head_gate:
+        if self.head_gate or self.element_gate:
             gate, gate_S = matmul_partials(rt, h, self.w_g, "head_gate")
         mask = {"chunk": self.chunk, "scale": self.scale}
         dmask = {"mask_chunk": self.chunk, "scale": self.scale}
-        tensor_cores = ops.mma_attention_usable(rt.dtype, hd) and rt.attention != "simt"
+        tensor_cores = (ops.mma_attention_usable(rt.dtype, hd) and rt.attention != "simt"
+                        and not self.exact and not self.pool)
         # one token per sequence on the tensor-core kernel, a small batch: that kernel sums the
         # product's slices, rotates and writes the cache row itself (no rotary kernel, one
         # hand-over less: 2-3 % of a step at batch 1, 0.5 % at 8 to 16; from 32 sequences on the
@@ -232,12 +316,37 @@ class GQAAttention:
             # this run reads the owner's keys and values: rotate q only
             scratch = rt.buffer("kv_step_unused", (n, 2, G, hd), rt.dtype)
             self.position.rotate_and_store(qkv, S, batch, view, q, scratch, H, G,
-                                           write_cache=False)
+                                           write_cache=False, **extras)
         else:
             self.position.rotate_and_store(qkv, S, batch, view, q, kv_step, H, G,
-                                           write_cache=not late_write)
+                                           write_cache=not late_write, **extras)
+        pooled = None
+        if self.pool:
+            # the blocks this step completes, before any query of the step looks at them (and
+            # before the late ring write, which may replace rows they are made of)
+            if not shared and view.capacity >= self.pool - 1:
+                ops.pool_blocks(kv_step, view.k, view.v, batch, view.slot_pos, pool_view.k, pool_view.v,
+                                G, hd, view.capacity, self.pool, pool_view.capacity, rt.status,
+                                pages=view.pages, pool_pages=pool_view.pages)
+            pooled = (pool_view.k, pool_view.v, self.pool, pool_view.capacity, pool_view.pages)
         o = rt.buffer("attn_out", (n, H * hd), rt.dtype)
-        if batch.is_decode:
+        if self.pool or (self.exact and not batch.is_decode):
+            # 32-bit scores, weights and sums over the window's rows and the pooled rows; a decode
+            # step's few queries are split over their keys so that the grid fills the device
+            bound = max(1, batch.ctx_bound)
+            visible = min(bound, self.span) if self.span else bound
+            if self.pool:
+                visible += bound // self.pool
+            nsplit = 1
+            if batch.is_decode:
+                blocks = n * G * -(-(H // G) // 4)
+                nsplit = max(1, min(-(-visible // 64), 2 * rt.sm_count // max(1, blocks), 64))
+            part_o = rt.buffer("attn_part_o", (n, H, nsplit, hd), torch.float32)
+            part_ml = rt.buffer("attn_part_ml", (n, H, nsplit, 2), torch.float32)
+            ops.attention(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
+                          view.capacity, self.window, nsplit, part_o, part_ml, pages=view.pages,
+                          pooled=pooled, **mask)
+        elif batch.is_decode:
             # one query per sequence, every key already in the cache
             bound = max(1, batch.ctx_bound)
             visible = min(bound, self.span) if self.span else bound
@@ -265,7 +374,7 @@ class GQAAttention:
                 ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
                                      part_ml, counters, rt.status, H, G, hd, view.capacity,
                                      self.window, chunk, bound, pages=view.pages, **dmask)
-        elif rt.attention in ("auto", "tcgen05") and ops.tc_attention_usable(
+        elif rt.attention in ("auto", "tcgen05") and not self.exact and ops.tc_attention_usable(
                 rt.dtype, hd, batch.past, batch.q_lens, view.capacity):
             # S, P and O in tensor memory, two query tiles per block in ping-pong (41 us
             # against 357 us for the mma.sync kernel per layer at 2,048 tokens of 32 heads
@@ -286,6 +395,8 @@ class GQAAttention:
                           view.capacity, self.window, 1, None, None, pages=view.pages, **mask)
         if self.head_gate:
             ops.head_gate(o, gate, gate_S, H, hd)
+        elif self.element_gate:
+            ops.head_gate(o, gate, gate_S, H * hd, 1)        # a "head" per feature
         stream.add_linear(o, self.w_o)
         if late_write:
             def write_ring():

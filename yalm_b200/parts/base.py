@@ -204,6 +204,32 @@ class ResidualStream:
         self.x = x
         self.pending: Optional[torch.Tensor] = None    # float32 [S, N, D]
         self.n_pending = 0
+        # A block that norms AFTER the sum (x <- n(a x + y)) sets ``hold``: products then never
+        # add into x; they leave their slices pending (``add_linear``), or a mixer made of
+        # branches leaves each branch's slices with the weight it is to be normed with and its
+        # factor (``add_branches``), and the block's norm forms the sum.
+        self.hold = False
+        self.branches: list = []                       # (slices [S, N, D], S, norm weight | None, factor)
+        self.branch_eps = 0.0
+        self.h: Optional[torch.Tensor] = None          # x in the compute type, while x is unchanged
+
+    def as_input(self) -> torch.Tensor:
+        """x itself as the input of a product: in the compute type (a copy that the last norm
+        made, or one made here), or x where the compute type is 32-bit."""
+        if self.rt.dtype == torch.float32:
+            return self.x
+        if self.h is None:
+            self.h = self.rt.buffer("stream_input", tuple(self.x.shape), self.rt.dtype)
+            ops.cast_rows(self.x, self.h)
+        return self.h
+
+    def add_branches(self, branches, eps: float) -> None:
+        """The mixer's output is sum_b factor_b n(B_b, w_b): left for the block's norm."""
+        if not self.hold:
+            raise RuntimeError("branches that are normed before the sum need a block that holds the sum")
+        if self.n_pending or self.branches:
+            raise RuntimeError("the stream already holds a pending output")
+        self.branches, self.branch_eps = list(branches), float(eps)
 
     def add_linear(self, a: torch.Tensor, w: torch.Tensor) -> None:
         """x += a @ w.T"""
@@ -211,6 +237,9 @@ class ResidualStream:
         matmul_into_stream(self.rt, a, w, self)
 
     def resolve(self) -> torch.Tensor:
+        if self.branches:
+            raise RuntimeError("normed branches are pending: only a norm that sums them can resolve the stream")
+        self.h = None
         if self.n_pending:
             self.x += self.pending[:self.n_pending].sum(0)
             self.pending, self.n_pending = None, 0
@@ -218,6 +247,7 @@ class ResidualStream:
 
     def add_tensor(self, y: torch.Tensor) -> None:
         """x += y, and the pending partial sums with it."""
+        self.h = None
         if y.dtype == torch.float32 and y.is_contiguous() and y.shape == self.x.shape \
                 and self.x.is_cuda:
             ops.residual_add(self.x, y, self.pending, self.n_pending)

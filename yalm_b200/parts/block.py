@@ -46,3 +46,45 @@ class PreNormBlock:
             h = self.ffn_norm(stream)
             self.ffn.forward(h, batch, stream)
         return later
+
+
+@register_block("postnorm")
+class PostNormBlock:
+    """Norm after the sum: x <- norm1(a x + mixer(x)); x <- norm2(a x + ffn(x)).  The sublayers
+    read x itself (in the compute type); the norms are of kind ``sum_rmsnorm``, which own the
+    factor a.  The feed-forward and its norm may be absent."""
+
+    def __init__(self, layer_spec, rt):
+        self.spec = layer_spec
+        self.mixer = make_part(MIXERS, layer_spec.part("mixer"), rt)
+        self.mixer_norm = make_part(NORMS, layer_spec.part("mixer_norm"), rt)
+        self.ffn = self.ffn_norm = None
+        if "feed_forward" in layer_spec.parts:
+            self.ffn = make_part(FEED_FORWARDS, layer_spec.part("feed_forward"), rt)
+            self.ffn_norm = make_part(NORMS, layer_spec.part("feed_forward_norm"), rt)
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not hasattr(n, "apply"):
+                raise TypeError("a postnorm block needs norms that form the sum themselves (sum_rmsnorm)")
+
+    def parts(self):
+        s = self.spec
+        out = [(self.mixer, s.part("mixer")), (self.mixer_norm, s.part("mixer_norm"))]
+        if self.ffn is not None:
+            out += [(self.ffn, s.part("feed_forward")), (self.ffn_norm, s.part("feed_forward_norm"))]
+        return out
+
+    def mixers(self):
+        return {"mixer": self.mixer}
+
+    def forward(self, stream, batch, views, shared: bool = False):
+        stream.resolve()
+        stream.hold = True
+        try:
+            later = self.mixer.forward(stream.as_input(), batch, stream, views["mixer"], shared=shared)
+            self.mixer_norm.apply(stream)
+            if self.ffn is not None:
+                self.ffn.forward(stream.as_input(), batch, stream)
+                self.ffn_norm.apply(stream)
+        finally:
+            stream.hold = False
+        return later

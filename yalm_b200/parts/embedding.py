@@ -28,6 +28,7 @@ class Embedding:
         self.rt = rt
         self.vocab = int(params["vocab_size"])
         self.size = int(params["size"])
+        self.scale = float(params.get("scale") or 1.0)       # x = E[token] * scale
         self.table = None
 
     def tensor_needs(self):
@@ -41,7 +42,7 @@ class Embedding:
 
     def forward(self, batch, view=None, keep_copy: bool = False):
         x = self.rt.buffer("residual", (batch.n_tokens, self.size), torch.float32)
-        ops.embed(batch.tokens, self.table, x, self.rt.status)
+        ops.embed(batch.tokens, self.table, x, self.rt.status, scale=self.scale)
         if keep_copy:
             copy = self.rt.buffer("embedding_output", (batch.n_tokens, self.size), torch.float32)
             copy.copy_(x)

@@ -147,8 +147,21 @@ def matmul_into_stream(rt, a: torch.Tensor, w: torch.Tensor, stream) -> None:
     """stream.x += a @ w.T, directly or as pending partial sums."""
     M, K = a.shape
     N = w.shape[0]
+    if getattr(stream, "hold", False):
+        # the block norms after the sum: the product stays apart from x until that norm
+        if stream.n_pending or stream.branches:
+            raise RuntimeError("the stream already holds a pending output")
+        if _use_tc(rt, a, w) and M > MANY_TOKENS and plan_splits_many(M, N, K, rt.sm_count) > 1:
+            S = plan_splits_many(M, N, K, rt.sm_count)       # few tiles: slices of K fill the idle pairs
+            buf = rt.buffer("stream_partials", (S, M, N), torch.float32)
+            ops.gemm_2sm(a, w, buf, ops.GEMM_SPLIT, rt.status, splits=S)
+            stream.pending, stream.n_pending = buf, S
+        else:
+            stream.pending, stream.n_pending = matmul_partials(rt, a, w, "stream_partials")
+        return
     if stream.n_pending:
         stream.resolve()
+    stream.h = None
     if _use_tc(rt, a, w):
         if _small(rt, M, N):
             S = plan_splits(M, N, K, rt.sm_count)

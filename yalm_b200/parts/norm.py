@@ -39,3 +39,40 @@ class RMSNorm:
         if rows is None:
             stream.pending, stream.n_pending = None, 0     # folded into x by the kernel
         return out
+
+
+@register_norm("sum_rmsnorm")
+class SumRMSNorm:
+    """The norm of a layer that norms AFTER the residual sum: x <- n(a x + y, w), with
+    n(v, w) = v / sqrt(mean(v^2) + eps) * w and ``a`` = ``residual_scale``.  y is what the
+    sublayer left on the stream: the slices of its last product, or the branches of a mixer
+    made of several (each normed with a weight of its own and scaled before the sum).  The new
+    x replaces the old in 32 bits; a copy in the compute type is left as ``stream.h`` for the
+    next sublayer, which reads x itself."""
+
+    def __init__(self, params: dict, rt):
+        self.rt = rt
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.alpha = float(params.get("residual_scale", 1.0))
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_needs(self):
+        return {"weight": TensorNeed((self.size,), init="ones")}
+
+    def bind(self, tensors) -> None:
+        self.weight = self.rt.vector(tensors["weight"])
+
+    def apply(self, stream: ResidualStream) -> None:
+        if stream.branches:
+            branches, beps = stream.branches, stream.branch_eps
+        elif stream.n_pending:
+            branches, beps = [(stream.pending, stream.n_pending, None, 1.0)], 0.0
+        else:
+            branches, beps = [], 0.0
+        h = None
+        if self.rt.dtype != torch.float32:
+            h = self.rt.buffer("stream_input", tuple(stream.x.shape), self.rt.dtype)
+        ops.sum_norm(stream.x, self.alpha, branches, self.weight, self.eps, h=h, branch_eps=beps)
+        stream.pending, stream.n_pending, stream.branches = None, 0, []
+        stream.h = h

@@ -101,3 +101,56 @@ class Rope:
 
 
 NoPosition.step_table = Rope.step_table
+
+
+def yarn_frequencies(dims: int, base: float, scaling: Optional[dict]):
+    """Angle per position of the dims/2 rotated pairs, f_i = base^(-2i/dims), and the factor on
+    cos and sin.  With ``scaling`` = {factor, original, fast, slow} (YaRN): pairs that turn fewer
+    than ``slow`` times over ``original`` positions are slowed down by ``factor``, pairs that
+    turn more than ``fast`` times stay, a linear ramp over the pair index between them, and cos
+    and sin are multiplied by 0.1 ln(factor) + 1."""
+    f = [float(base) ** (-2.0 * i / dims) for i in range(dims // 2)]
+    mult = 1.0
+    if scaling:
+        factor, orig = float(scaling["factor"]), float(scaling["original"])
+        where = lambda turns: dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+        lo = max(math.floor(where(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(where(float(scaling["slow"]))), dims - 1)
+        for i in range(dims // 2):
+            ramp = min(1.0, max(0.0, (i - lo) / max(hi - lo, 0.001)))
+            f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp)
+        mult = 0.1 * math.log(factor) + 1.0
+    return torch.tensor(f, dtype=torch.float64).to(torch.float32), mult
+
+
+@register_position("rope_partial")
+class PartialRope:
+    """Rotation of the first ``dims`` features of every head (the rest pass unchanged), in pairs
+    (i, i + dims/2) (``layout`` "halves") or (2i, 2i + 1) ("neighbours"), by pos * f_i with
+    optional YaRN scaling; the angle is formed in 32 bits inside the kernel.  Its kernel also
+    norms q and k over their whole projections first when the mixer hands it the weights
+    (``norms``), and takes the values from the keys as projected when the product has no v
+    rows (``has_v`` False).  It has no per-step table: the mixer's products stay apart from it."""
+
+    def __init__(self, params: dict, rt):
+        self.rt = rt
+        self.head_dim = int(params["head_dim"])
+        self.dims = int(params.get("dims", self.head_dim))
+        self.neighbours = params.get("layout", "halves") == "neighbours"
+        if params.get("layout", "halves") not in ("halves", "neighbours"):
+            raise ValueError(f"rope_partial: layout {params.get('layout')!r} (halves or neighbours)")
+        if self.dims % 2 or not 0 <= self.dims <= self.head_dim:
+            raise ValueError(f"rope_partial: {self.dims} rotated features of a head of {self.head_dim}")
+        if self.dims:
+            freq, self.mult = yarn_frequencies(self.dims, float(params["base"]), params.get("scaling"))
+        else:
+            freq, self.mult = torch.zeros(1), 1.0
+        self.freq = freq.to(rt.device)
+
+    def rotate_and_store(self, qkv, n_partials, batch, view, q_out, kv_step, H, G, write_cache=True,
+                         norms=None, has_v=True) -> None:
+        qn, kn, n_q, n_k, eps = norms if norms is not None else (None, None, 1, 1, 0.0)
+        ops.qk_norm_rope_store(qkv, n_partials, qn, kn, n_q, n_k, eps, self.freq, self.dims,
+                               self.neighbours, self.mult, batch, q_out, kv_step, view.k, view.v,
+                               view.slot_pos, H, G, self.head_dim, has_v, view.capacity, write_cache,
+                               pages=view.pages)
