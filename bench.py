@@ -353,19 +353,61 @@ DESIGN_SIZES = {
 }
 
 
+def rudazen_config(width, heads, kv_heads, head_dim, window, pool, rot_dims, rec_heads, rec_dim, rec_vdim,
+                   ff, pattern, vocab):
+    """A Rudazen configuration with layers of the sizes a served model has (random weights):
+    ``pattern`` is a string of "p" (a parallel layer) and "a" (an attention layer with pooled blocks)."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5}
+    pooled = dict(att, mask={"size": window, "pool": pool}, rot={"base": 1e6, "dims": head_dim})
+    left = dict(att, mask={"size": window},
+                rot={"base": 1e4, "dims": rot_dims,
+                     "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}})
+    right = {"heads": rec_heads, "dim": rec_dim, "vdim": rec_vdim}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp} if c == "p" else
+              {"type": "attention", "mixer": pooled, "mlp": mlp} for c in pattern]
+    return {"architecture": "Rudazen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "postln_alpha": 2.0, "embedding": {"scale": float(width) ** 0.5}, "layers": layers}
+
+
+def rudazen_twin(width, heads, kv_heads, head_dim, window, pool, rot_dims, rec_heads, rec_dim, rec_vdim, ff,
+                 pattern, vocab):
+    """The closest model the library had before: the Llama / Mistral decoder with the same width,
+    heads, layers and feed-forward and a sliding window of the same size."""
+    return {"architectures": ["MistralForCausalLM"], "hidden_size": width, "intermediate_size": ff,
+            "num_hidden_layers": len(pattern), "num_attention_heads": heads, "num_key_value_heads": kv_heads,
+            "head_dim": head_dim, "vocab_size": vocab, "max_position_embeddings": 32768, "rms_norm_eps": 1e-6,
+            "rope_theta": 10000.0, "sliding_window": window, "tie_word_embeddings": False,
+            "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2}
+
+
+RUDAZEN_SIZES = {
+    "w2048-ppa": dict(width=2048, heads=16, kv_heads=4, head_dim=128, window=1024, pool=64, rot_dims=64,
+                      rec_heads=16, rec_dim=128, rec_vdim=128, ff=5632, pattern="paapaa", vocab=32000),
+    "w4096-pa": dict(width=4096, heads=32, kv_heads=8, head_dim=128, window=2048, pool=64, rot_dims=64,
+                     rec_heads=32, rec_dim=128, rec_vdim=128, ff=11008, pattern="paap", vocab=32000),
+}
+DESIGNS = {"golulix": (DESIGN_SIZES, golulix_config, dense_twin),
+           "rudazen": (RUDAZEN_SIZES, rudazen_config, rudazen_twin)}
+
+
 def compare_designs(args, pk):
-    """Prefill and decode of the Golulix design beside the dense decoder at equal sizes: tokens/s,
+    """Prefill and decode of a design (--design) beside the dense decoder at equal sizes: tokens/s,
     and how far each is from its roofline (prefill: floating-point operations over the measured
     matrix-product peak; decode: bytes that must be read over the measured copy rate)."""
     import torch
     from yalm_b200 import LM
-    out = {"compare": "golulix vs the dense decoder at equal sizes", "dtype": args.dtype,
+    all_sizes, make, twin = DESIGNS[args.design]
+    out = {"compare": f"{args.design} vs the dense decoder at equal sizes", "dtype": args.dtype,
            "peaks": pk["source"], "sizes": {}}
-    names = [args.design_size] if args.design_size else list(DESIGN_SIZES)
+    if args.design_size and args.design_size not in all_sizes:
+        print(f"bench.py: --design {args.design} has the sizes {sorted(all_sizes)}")
+        return 2
+    names = [args.design_size] if args.design_size else list(all_sizes)
     for name in names:
-        sizes = DESIGN_SIZES[name]
+        sizes = all_sizes[name]
         rec = {}
-        for who, cfg in (("golulix", golulix_config(**sizes)), ("dense", dense_twin(**sizes))):
+        for who, cfg in ((args.design, make(**sizes)), ("dense", twin(**sizes))):
             lm = LM.from_random(cfg, seed=0, dtype=args.dtype, std=0.02, norm_jitter=0.0,
                                 max_context=4096, max_batch=64)
             torch.cuda.synchronize()
@@ -390,8 +432,8 @@ def compare_designs(args, pk):
             torch.cuda.empty_cache()
         rec["roofline_distance_ratio"] = {
             k: (rec["dense"][k].get("roofline_frac") or rec["dense"][k]["hbm_frac"]) /
-               (rec["golulix"][k].get("roofline_frac") or rec["golulix"][k]["hbm_frac"])
-            for k in rec["golulix"] if k != "weights_gb"}
+               (rec[args.design][k].get("roofline_frac") or rec[args.design][k]["hbm_frac"])
+            for k in rec[args.design] if k != "weights_gb"}
         out["sizes"][name] = rec
     print(json.dumps(out))
     return 0
@@ -484,10 +526,12 @@ def main():
                     help="warps per block of the tensor-core decode attention (default: the "
                          "attention part decides by the batch)")
     ap.add_argument("--compare-designs", action="store_true",
-                    help="instead of the default workload: prefill and decode of the Golulix design "
+                    help="instead of the default workload: prefill and decode of a second design (--design) "
                          "beside the dense decoder at equal sizes (random weights, a few layers)")
-    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES),
-                    help="with --compare-designs: one of the sizes instead of all")
+    ap.add_argument("--design", default="golulix", choices=sorted(DESIGNS),
+                    help="with --compare-designs: which design runs beside the dense decoder")
+    ap.add_argument("--design-size", default=None, choices=sorted(set(DESIGN_SIZES) | set(RUDAZEN_SIZES)),
+                    help="with --compare-designs: one of the design's sizes instead of all")
     args = ap.parse_args()
 
     if args.impl == "reference":

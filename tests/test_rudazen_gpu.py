@@ -191,7 +191,7 @@ def test_pooled_blocks_beside_a_window(ops, window, pool, cap, dt):
         assert not bad.numel(), f"sequence {s}: first wrong position {int(bad[0])} (window {window}, pool {pool})"
 
 
-@pytest.mark.parametrize("H, dk, dv", [(3, 24, 16), (1, 8, 40), (2, 20, 12), (2, 128, 64)])
+@pytest.mark.parametrize("H, dk, dv", [(3, 24, 16), (1, 8, 40), (2, 20, 12), (2, 128, 64), (1, 200, 9), (2, 64, 128)])
 def test_gated_recurrence_in_portions(ops, H, dk, dv):
     g = torch.Generator().manual_seed(dk)
     D = 32
@@ -213,7 +213,8 @@ def test_gated_recurrence_in_portions(ops, H, dk, dv):
         proj = (hcat @ wcat.T)
         parts = torch.stack([0.25 * proj, 0.75 * proj]).contiguous().to(DEV)
         out = torch.empty(b.n_tokens, H * dv, device=DEV)
-        ops.gated_recurrence(parts, 2, w["r.f.b"].to(DEV), w["r.lower"].to(DEV), b, state, out, H, dk, dv)
+        act = torch.empty(b.n_tokens, 2 * H * dk + H * dv, device=DEV)
+        ops.gated_recurrence(parts, 2, w["r.f.b"].to(DEV), w["r.lower"].to(DEV), b, state, out, H, dk, dv, act)
         normed = torch.empty(b.n_tokens, H * dv, device=DEV)
         ops.head_norm(out, w["r.norm"].to(DEV), normed, H, dv, 1e-5)
         qs = b.q_start.tolist()

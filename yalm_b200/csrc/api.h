@@ -228,12 +228,13 @@ int yalm_head_norm(const float* o, const float* w, void* out, int out_dtype, lon
 
 // ---- recurrence.cu: S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t per head ------
 // proj: float32 slices [n_partials][tokens][2 H dk + H dv] = (q | f | v) before activation:
-// q = silu(.), f = lower + (1 - lower) sigmoid(. + f_bias); state [slots][H][dk][dv] float32;
-// out float32 [tokens][H dv]
+// q = silu(.), f = lower + (1 - lower) sigmoid(. + f_bias); act: float32 scratch of one slice's
+// size (the activated projection, written by a first kernel and read by the scan); state
+// [slots][H][dk][dv] float32; out float32 [tokens][H dv]
 int yalm_gated_recurrence(const float* proj, int n_partials, long long partial_stride,
-                          const float* f_bias, const float* lower, const int* q_start,
-                          const int* seq_slot, float* state, float* out, int n_seqs, int H, int dk,
-                          int dv, cudaStream_t stream);
+                          const float* f_bias, const float* lower, float* act, const int* q_start,
+                          const int* seq_slot, float* state, float* out, int n_tokens, int n_seqs,
+                          int H, int dk, int dv, cudaStream_t stream);
 
 // ---- small_ops.cu ---------------------------------------------------------------------
 // x[t] = E[token t] + P[row t] (also into x_copy when given): row = buckets for a sequence's

@@ -103,7 +103,7 @@ _SIGNATURES = {
                       _i, _vp],
     "yalm_cast_rows": [_vp, _vp, _i, _ll, _vp],
     "yalm_head_norm": [_vp, _vp, _vp, _i, _ll, _i, _i, _f, _vp],
-    "yalm_gated_recurrence": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "yalm_gated_recurrence": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
 }
 
 _lib = None
@@ -766,10 +766,12 @@ def head_norm(o: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: i
 
 
 def gated_recurrence(proj: torch.Tensor, n_partials: int, f_bias: torch.Tensor, lower: torch.Tensor,
-                     batch, state: torch.Tensor, out: torch.Tensor, H: int, dk: int, dv: int) -> None:
+                     batch, state: torch.Tensor, out: torch.Tensor, H: int, dk: int, dv: int,
+                     act: torch.Tensor) -> None:
     """S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t per head over a step's tokens, from
     the fused projection (q | f | v) as float32 slices [(s,) N, 2 H dk + H dv]; ``state`` float32
-    [slots, H, dk, dv] is read at the step's start and written at its end; out float32 [N, H dv]."""
+    [slots, H, dk, dv] is read at the step's start and written at its end; out float32 [N, H dv];
+    ``act``: float32 scratch [N, 2 H dk + H dv] for the activated projection (two launches)."""
     n = out.shape[0]
     row = 2 * H * dk + H * dv
     _need(proj.dtype == torch.float32 and proj.is_contiguous() and proj.shape[-1] == row
@@ -779,9 +781,11 @@ def gated_recurrence(proj: torch.Tensor, n_partials: int, f_bias: torch.Tensor, 
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv)
           and out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == H * dv,
           "gated_recurrence: state float32 [slots, H, dk, dv], out float32 [N, H dv]")
-    _check(lib().yalm_gated_recurrence(_p(proj), n_partials, n * row, _p(f_bias), _p(lower),
-                                       _p(batch.q_start), _p(batch.seq_slot), _p(state), _p(out),
-                                       batch.n_seqs, H, dk, dv, _stream()), "gated_recurrence")
+    _need(act.dtype == torch.float32 and act.is_contiguous() and act.numel() >= n * row,
+          "gated_recurrence: act float32 [N, 2 H dk + H dv]")
+    _check(lib().yalm_gated_recurrence(_p(proj), n_partials, n * row, _p(f_bias), _p(lower), _p(act),
+                                       _p(batch.q_start), _p(batch.seq_slot), _p(state), _p(out), n,
+                                       batch.n_seqs, H, dk, dv, _stream()), "gated_recurrence", kernels=2)
 
 
 # ---- a routed feed-forward --------------------------------------------------------------

@@ -70,7 +70,8 @@ class GatedLinearRecurrence:
         n = batch.n_tokens
         proj, S = matmul_partials(rt, h, self.w_qfv, "recurrence_qfv")
         o = rt.buffer("recurrence_out", (n, H * dv), torch.float32)
-        ops.gated_recurrence(proj, S, self.f_bias, self.lower, batch, view.state, o, H, dk, dv)
+        act = rt.buffer("recurrence_act", (n, 2 * H * dk + H * dv), torch.float32)
+        ops.gated_recurrence(proj, S, self.f_bias, self.lower, batch, view.state, o, H, dk, dv, act)
         on = rt.buffer("recurrence_normed", (n, H * dv), rt.dtype)
         ops.head_norm(o, self.norm, on, H, dv, self.eps)
         stream.add_linear(on, self.w_o)
