@@ -248,6 +248,9 @@ int yalm_embed_pair(const int* tokens, const int* token_seq, const int* q_start,
 // o [n, H, hd] *= sigmoid(sum of the n_partials slices of g [n, H])
 int yalm_head_gate(void* o, int dtype, const float* g, int n_partials, long long partial_stride,
                    int n_tokens, int H, int hd, cudaStream_t stream);
+// o [n] *= sigmoid(sum of the n_partials slices of g [n]), feature by feature (n % 4 == 0)
+int yalm_element_gate(void* o, int dtype, const float* g, int n_partials, long long partial_stride,
+                      long long n, cudaStream_t stream);
 // v <- cap * tanh(v / cap) over n floats
 int yalm_softcap(float* v, long long n, float cap, cudaStream_t stream);
 // x += y + sum of n_partials slices, n floats each

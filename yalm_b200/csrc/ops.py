@@ -82,6 +82,7 @@ _SIGNATURES = {
                         _vp, _vp],
     "yalm_head_gate": [_vp, _i, _vp, _i, _ll, _i, _i, _i, _vp],
     "yalm_softcap": [_vp, _ll, _f, _vp],
+    "yalm_element_gate": [_vp, _i, _vp, _i, _ll, _ll, _vp],
     "yalm_residual_add": [_vp, _vp, _vp, _i, _ll, _ll, _vp],
     "yalm_route_topk": [_vp, _i, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "yalm_route_plan": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -654,6 +655,18 @@ def head_gate(o: torch.Tensor, g: torch.Tensor, n_partials: int, H: int, hd: int
           and g.numel() >= n_partials * n * H, "head_gate: shapes")
     _check(lib().yalm_head_gate(_p(o), dtype_code(o.dtype), _p(g), n_partials, n * H, n, H, hd, _stream()),
            "head_gate")
+
+
+def element_gate(o: torch.Tensor, g: torch.Tensor, n_partials: int) -> None:
+    """o [n, F] *= sigmoid(g) feature by feature; g float32 [n_partials, n, F] slices that are summed."""
+    n = o.numel()
+    _need(o.is_contiguous() and g.dtype == torch.float32 and g.is_contiguous()
+          and g.numel() >= n_partials * n, "element_gate: shapes")
+    if n % 4 or g.data_ptr() % 16:
+        head_gate(o, g, n_partials, o.shape[1], 1)       # odd sizes: a "head" per feature
+        return
+    _check(lib().yalm_element_gate(_p(o), dtype_code(o.dtype), _p(g), n_partials, n, n, _stream()),
+           "element_gate")
 
 
 def softcap(v: torch.Tensor, cap: float) -> None:

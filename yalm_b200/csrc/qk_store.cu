@@ -28,7 +28,7 @@ __global__ void qk_norm_rope_store_kernel(
     T* __restrict__ kv_step, T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G, int hd,
     int has_v, int capacity, int write_cache, const int* __restrict__ page_table, int pps, int n_pages) {
   pdl_launch_dependents();
-  extern __shared__ float row_s[];                       // the summed row
+  extern __shared__ float row_s[];                       // the summed row, then dims / 2 (cos, sin) pairs
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   const int b = token_seq[t];
@@ -41,6 +41,12 @@ __global__ void qk_norm_rope_store_kernel(
   const int nq = H * hd, nk = G * hd;
   const int row = nq + nk + (has_v ? nk : 0);
   const float* src = qkv + (size_t)t * row;
+  // the token's cosines and sines, once for all heads (the angle in 32 bits)
+  float2* cs = reinterpret_cast<float2*>(row_s + ((row + 1) & ~1));
+  for (int i = threadIdx.x; i < (dims >> 1); i += blockDim.x) {
+    const float ang = (float)pos * freq[i];
+    cs[i] = make_float2(cosf(ang) * mult, sinf(ang) * mult);
+  }
   float ssq = 0.f, ssk = 0.f;
   for (int i = threadIdx.x; i < row; i += blockDim.x) {
     const float v = sum_slices(src + i, n_partials, partial_stride);
@@ -69,8 +75,7 @@ __global__ void qk_norm_rope_store_kernel(
       const int ip = i - e + pi;
       const int jp = j - e + pi;
       const float other = row_s[ip] * (w != nullptr ? r * w[jp] : 1.f);
-      const float ang = (float)pos * freq[pair];
-      const float c = cosf(ang) * mult, s = sinf(ang) * mult;
+      const float c = cs[pair].x, s = cs[pair].y;
       me = first ? rotate_lo(me, other, c, s) : rotate_hi(other, me, c, s);
     }
     const T val = from_float<T>(me);
@@ -155,7 +160,7 @@ extern "C" int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long lo
   if (n_tokens <= 0) return 0;
   if (hd <= 0 || dims < 0 || dims > hd || (dims & 1) || H <= 0 || G <= 0 || n_q <= 0 || n_k <= 0) return -2;
   const int row = (H + (has_v ? 2 : 1) * G) * hd;
-  const size_t smem = (size_t)row * sizeof(float);
+  const size_t smem = (size_t)(((row + 1) & ~1) + dims) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   const int threads = row >= 2048 ? 512 : (row >= 512 ? 256 : 128);
 #define YALM_QKS(T)                                                                                   \

@@ -22,16 +22,16 @@ constexpr int RC_COLS = 8 * RC_CPW;       // ... per block of eight warps
 constexpr int RC_TOK = 16;
 constexpr int RC_STAGES = 3;
 
+// One block per token; a thread walks the row with its own stride.
 __global__ void recurrence_gates_kernel(const float* __restrict__ proj, int n_partials,
                                         long long partial_stride, const float* __restrict__ f_bias,
                                         const float* __restrict__ lower, float* __restrict__ act,
-                                        long long total, int row, int n_q) {
+                                        int row, int n_q) {
   pdl_launch_dependents();
   pdl_wait();
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const int e = (int)(idx % row);
-    const float z = sum_slices(proj + idx, n_partials, partial_stride);
+  const size_t base = (size_t)blockIdx.x * row;
+  for (int e = threadIdx.x; e < row; e += blockDim.x) {
+    const float z = sum_slices(proj + base + e, n_partials, partial_stride);
     float v = z;
     if (e < n_q) {
       v = z / (1.0f + expf(-z));
@@ -39,7 +39,7 @@ __global__ void recurrence_gates_kernel(const float* __restrict__ proj, int n_pa
       const float l = lower[e - n_q];
       v = l + (1.0f - l) * (1.0f / (1.0f + expf(-(z + f_bias[e - n_q]))));
     }
-    act[idx] = v;
+    act[base + e] = v;
   }
 }
 
@@ -190,11 +190,8 @@ extern "C" int yalm_gated_recurrence(const float* proj, int n_partials, long lon
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
   if (H <= 0 || dk <= 0 || dv <= 0 || dk > 256 || n_seqs > 65535 || H > 65535) return -2;
   const int row = 2 * H * dk + H * dv;
-  const long long total = (long long)n_tokens * row;
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  launch_pdl(recurrence_gates_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, proj, n_partials,
-             partial_stride, f_bias, lower, act, total, row, H * dk);
+  launch_pdl(recurrence_gates_kernel, dim3(n_tokens), dim3(row >= 2048 ? 512 : 256), 0, stream, proj,
+             n_partials, partial_stride, f_bias, lower, act, row, H * dk);
   YALM_LAUNCH_CHECK();
   const dim3 grid((dv + RC_COLS - 1) / RC_COLS, H, n_seqs), block(256);
   const int rpt = (dk + 31) / 32;

@@ -85,6 +85,27 @@ __global__ void head_gate_kernel(T* __restrict__ o, const float* __restrict__ g,
     row[i] = from_float<T>(to_float(row[i]) * gate_s[i / hd]);
 }
 
+// o [n] *= sigmoid(sum over slices of g [S][n]), feature by feature; four features per thread
+template <typename T>
+__global__ void element_gate_kernel(T* __restrict__ o, const float* __restrict__ g, int n_partials,
+                                    long long partial_stride, long long n4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_partials; ++s) {
+      const float4 p = *reinterpret_cast<const float4*>(g + (size_t)s * partial_stride + 4 * i);
+      z.x += p.x; z.y += p.y; z.z += p.z; z.w += p.w;
+    }
+    T* e = o + 4 * i;
+    e[0] = from_float<T>(to_float(e[0]) / (1.0f + expf(-z.x)));
+    e[1] = from_float<T>(to_float(e[1]) / (1.0f + expf(-z.y)));
+    e[2] = from_float<T>(to_float(e[2]) / (1.0f + expf(-z.z)));
+    e[3] = from_float<T>(to_float(e[3]) / (1.0f + expf(-z.w)));
+  }
+}
+
 __global__ void softcap_kernel(float* __restrict__ v, long long n, float cap) {
   pdl_launch_dependents();
   pdl_wait();
@@ -149,6 +170,22 @@ extern "C" int yalm_head_gate(void* o, int dtype, const float* g, int n_partials
     launch_pdl(head_gate_kernel<__half>, grid, block, smem, stream, (__half*)o, g, n_partials, partial_stride, H, hd);
   else
     return -3;
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+// o [n] *= sigmoid(sum of the n_partials slices of g [n]); n a multiple of 4, g 16-byte aligned
+extern "C" int yalm_element_gate(void* o, int dtype, const float* g, int n_partials,
+                                 long long partial_stride, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n % 4 != 0 || partial_stride % 4 != 0 || (((uintptr_t)g) & 15)) return -2;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const dim3 grid((unsigned)blocks), block(256);
+  if (dtype == DT_F32) launch_pdl(element_gate_kernel<float>, grid, block, 0, stream, (float*)o, g, n_partials, partial_stride, n / 4);
+  else if (dtype == DT_BF16) launch_pdl(element_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, (__nv_bfloat16*)o, g, n_partials, partial_stride, n / 4);
+  else if (dtype == DT_F16) launch_pdl(element_gate_kernel<__half>, grid, block, 0, stream, (__half*)o, g, n_partials, partial_stride, n / 4);
+  else return -3;
   YALM_LAUNCH_CHECK();
   return 0;
 }

@@ -72,6 +72,100 @@ sum_norm_kernel(float* __restrict__ x, float alpha, SumBranch b0, SumBranch b1, 
   }
 }
 
+// The same with four neighbouring features per thread and step (dim % 4 == 0, 16-byte aligned
+// pointers): every load of a pass is in flight at once.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 sum_slices4(const float* p, int n, long long stride) {
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s0 = 0; s0 < n; s0 += 4) {
+    float4 t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) t[j] = s0 + j < n ? ld4(p + (size_t)(s0 + j) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
+  }
+  return v;
+}
+__device__ __forceinline__ float sq4(float4 v) { return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <typename T16> __device__ __forceinline__ void st4(T16* p, float4 v) {
+  uint2 u;
+  u.x = pack2<T16>(v.x, v.y);
+  u.y = pack2<T16>(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TO, int VPT>
+__global__ void __launch_bounds__(1024)
+sum_norm_vec_kernel(float* __restrict__ x, float alpha, SumBranch b0, SumBranch b1, int n_branches,
+                    float branch_eps, const float* __restrict__ weight, float eps, TO* __restrict__ h,
+                    int dim) {
+  pdl_launch_dependents();
+  const int nvec = dim >> 2;
+  float4 w[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {                       // the weights do not depend on the previous kernel
+    const int c = threadIdx.x + k * blockDim.x;
+    w[k] = c < nvec ? ld4(weight + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t r0 = (size_t)blockIdx.x * dim;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 u0[VPT], u1[VPT], v[VPT];
+  float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    u0[k] = (n_branches > 0 && c < nvec) ? sum_slices4(b0.p + r0 + 4 * c, b0.n, b0.stride) : zero;
+    u1[k] = (n_branches > 1 && c < nvec) ? sum_slices4(b1.p + r0 + 4 * c, b1.n, b1.stride) : zero;
+    v[k] = c < nvec ? ld4(x + r0 + 4 * c) : zero;
+    ss0 += sq4(u0[k]);
+    ss1 += sq4(u1[k]);
+  }
+  float rs0 = 1.f, rs1 = 1.f;
+  if (n_branches > 0 && b0.w != nullptr) rs0 = 1.0f / sqrtf(block_sum(ss0, scratch) / (float)dim + branch_eps);
+  if (n_branches > 1 && b1.w != nullptr) rs1 = 1.0f / sqrtf(block_sum(ss1, scratch) / (float)dim + branch_eps);
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < nvec) {
+      float4 a = zero;
+      if (n_branches > 0) {
+        float4 t = u0[k];
+        if (b0.w != nullptr) {
+          const float4 bw = ld4(b0.w + 4 * c);
+          t = make_float4(t.x * rs0 * bw.x, t.y * rs0 * bw.y, t.z * rs0 * bw.z, t.w * rs0 * bw.w);
+        }
+        a = make_float4(t.x * b0.scale, t.y * b0.scale, t.z * b0.scale, t.w * b0.scale);
+      }
+      if (n_branches > 1) {
+        float4 t = u1[k];
+        if (b1.w != nullptr) {
+          const float4 bw = ld4(b1.w + 4 * c);
+          t = make_float4(t.x * rs1 * bw.x, t.y * rs1 * bw.y, t.z * rs1 * bw.z, t.w * rs1 * bw.w);
+        }
+        a.x += t.x * b1.scale; a.y += t.y * b1.scale; a.z += t.z * b1.scale; a.w += t.w * b1.scale;
+      }
+      v[k] = make_float4(fmaf(alpha, v[k].x, a.x), fmaf(alpha, v[k].y, a.y), fmaf(alpha, v[k].z, a.z),
+                         fmaf(alpha, v[k].w, a.w));
+    }
+    ss += sq4(v[k]);
+  }
+  const float rs = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < nvec) {
+      const float4 y = make_float4(v[k].x * rs * w[k].x, v[k].y * rs * w[k].y, v[k].z * rs * w[k].z,
+                                   v[k].w * rs * w[k].w);
+      st4(x + r0 + 4 * c, y);
+      if (h != nullptr) st4(h + r0 + 4 * c, y);
+    }
+  }
+}
+
 template <typename TO>
 __global__ void cast_rows_kernel(const float* __restrict__ x, TO* __restrict__ out, long long n) {
   pdl_launch_dependents();
@@ -119,6 +213,29 @@ extern "C" int yalm_sum_norm(float* x, float alpha, int n_branches, const float*
   if (rows <= 256) {                                  // a few rows: one element per thread where that fits
     threads = (dim + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;
+  }
+  const bool vec = dim % 4 == 0 && s0 % 4 == 0 && s1 % 4 == 0 &&
+                   ((((uintptr_t)x) | ((uintptr_t)p0) | ((uintptr_t)p1) | ((uintptr_t)w0) | ((uintptr_t)w1) |
+                     ((uintptr_t)weight) | ((uintptr_t)h)) & 15) == 0;
+  if (vec) {
+    const int nvec = dim / 4;
+    int vt;                                             // few rows: one vector per thread; many: two
+    if (rows <= 256 || nvec <= 256) vt = nvec <= 1024 ? (nvec + 31) / 32 * 32 : 1024;
+    else vt = ((nvec + 1) / 2 + 31) / 32 * 32;
+    if (vt > 1024) vt = 1024;
+    const int vpt = (nvec + vt - 1) / vt;
+    void* hh = (h == nullptr) ? nullptr : h;
+#define YALM_SNV(T, V)                                                                                 \
+  launch_pdl(sum_norm_vec_kernel<T, V>, dim3(rows), dim3(vt), 0, stream, x, alpha, b0, b1, n_branches, \
+             branch_eps, weight, eps, (T*)hh, dim)
+    const int dt = h == nullptr ? DT_F32 : h_dtype;
+    if (dt == DT_F32) { if (vpt <= 1) YALM_SNV(float, 1); else YALM_SNV(float, 2); }
+    else if (dt == DT_BF16) { if (vpt <= 1) YALM_SNV(__nv_bfloat16, 1); else YALM_SNV(__nv_bfloat16, 2); }
+    else if (dt == DT_F16) { if (vpt <= 1) YALM_SNV(__half, 1); else YALM_SNV(__half, 2); }
+    else return -3;
+#undef YALM_SNV
+    YALM_LAUNCH_CHECK();
+    return 0;
   }
   const dim3 grid(rows), block(threads);
   if (h == nullptr || h_dtype == DT_F32)

@@ -396,7 +396,7 @@ class GQAAttention:
         if self.head_gate:
             ops.head_gate(o, gate, gate_S, H, hd)
         elif self.element_gate:
-            ops.head_gate(o, gate, gate_S, H * hd, 1)        # a "head" per feature
+            ops.element_gate(o, gate, gate_S)
         stream.add_linear(o, self.w_o)
         if late_write:
             def write_ring():
