@@ -417,7 +417,9 @@ def compare_designs(args, pk):
                 # the step's bound: its operations at the matrix-product peak, or its weights (every
                 # expert the tokens reach) at the copy rate, whichever takes longer
                 t_flops = prefill_flops(lm, T) / (pk["bf16_tflops"] * 1e12)
-                t_bytes = lm.model.step_bytes([1] * T) / (pk["hbm_gbs"] * 1e9)
+                # (a routed design reaches more experts with more tokens: one "sequence" per token
+                # counts that; any other design reads its weights once and one sequence's state)
+                t_bytes = lm.model.step_bytes([1] * T if args.design == "golulix" else [T]) / (pk["hbm_gbs"] * 1e9)
                 r[f"prefill_{T}"] = {"tokens_s": p["value"], "ms": p["ms"], "flops_frac": p["frac"],
                                      "bound": "flops" if t_flops >= t_bytes else "hbm",
                                      "roofline_frac": max(t_flops, t_bytes) / (p["ms"] / 1e3)}
