@@ -191,6 +191,44 @@ def test_pooled_blocks_beside_a_window(ops, window, pool, cap, dt):
         assert not bad.numel(), f"sequence {s}: first wrong position {int(bad[0])} (window {window}, pool {pool})"
 
 
+@pytest.mark.parametrize("hd, window, pool", [(32, 40, 8), (64, 100, 16), (128, 70, 0), (64, 0, 0)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_tensor_core_attention_with_unrounded_weights(ops, hd, window, pool, dt):
+    """Against the FMA kernel on the same cache: a first step fills ring and pooled rows, a second
+    brings several tokens on top (one sequence from its first token, one that goes on)."""
+    g = torch.Generator().manual_seed(hd + window)
+    H, G, cap = 4, 2, max(window, pool) or 256
+    pcap = 64
+    kc, vc = torch.zeros(3, G, cap, hd, dtype=dt, device=DEV), torch.zeros(3, G, cap, hd, dtype=dt, device=DEV)
+    pk, pv = torch.zeros(3, G, pcap, hd, dtype=dt, device=DEV), torch.zeros(3, G, pcap, hd, dtype=dt, device=DEV)
+    slot_pos = torch.zeros(3, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pooled = (pk, pv, pool, pcap, None) if pool else None
+    for q_lens, slots in (([37], [2]), ([90, 75], [0, 2]), ([3, 130], [0, 2])):
+        b = B(q_lens, slots)
+        n = b.n_tokens
+        q = torch.randn(n, H * hd, generator=g).to(dt).to(DEV)
+        kv = torch.randn(n, 2, G, hd, generator=g).to(dt).to(DEV)
+        past = {s: int(slot_pos[s]) for s in slots}
+        late = any(past[s] > 0 and ql > 1 and past[s] + ql > cap for s, ql in zip(slots, q_lens))
+        if not late:
+            ops.cache_write(kv, b, kc, vc, slot_pos, G, hd, cap)
+        if pool:
+            ops.pool_blocks(kv, kc, vc, b, slot_pos, pk, pv, G, hd, cap, pool, pcap, status)
+        ref, got = torch.empty(n, H * hd, dtype=dt, device=DEV), torch.empty(n, H * hd, dtype=dt, device=DEV)
+        ops.attention(q, kv, kc, vc, b, slot_pos, ref, H, G, hd, cap, window or None, 1, None, None, scale=0.2,
+                      pooled=pooled)
+        ops.attention_exact_prefill(q, kv, kc, vc, b, slot_pos, got, H, G, hd, cap, window or None, scale=0.2,
+                                    pooled=pooled)
+        if late:
+            ops.cache_write(kv, b, kc, vc, slot_pos, G, hd, cap)
+        ops.advance(b, slot_pos)
+        err = (got.float() - ref.float()).abs().max(-1).values
+        bad = (err > 2 ** -7 * ref.float().abs().max()).nonzero()
+        assert not bad.numel(), f"step {q_lens}: first wrong token {int(bad[0])}, error {float(err.max()):.3e}"
+    assert status.item() == 0
+
+
 @pytest.mark.parametrize("H, dk, dv", [(3, 24, 16), (1, 8, 40), (2, 20, 12), (2, 128, 64), (1, 200, 9), (2, 64, 128)])
 def test_gated_recurrence_in_portions(ops, H, dk, dv):
     g = torch.Generator().manual_seed(dk)
@@ -287,10 +325,12 @@ def test_a_request_does_not_depend_on_its_batch(dtype):
 
 # ------------------------------------------------------------------ one key that stands out
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kind, size, pool", [("attention", 9, 4), ("attention", 64, 16), ("attention", 70, 64),
-                                              ("parallel", 9, None), ("parallel", 64, None), ("parallel", 130, None)])
-def test_edges_of_windows_and_pooled_blocks(kind, size, pool, dtype):
-    cfg, w = needle_model(kind, size, pool)
+@pytest.mark.parametrize("kind, size, pool, dim", [("attention", 9, 4, 16), ("attention", 64, 16, 32),
+                                                   ("attention", 70, 64, 16), ("attention", 30, 7, 64),
+                                                   ("parallel", 9, None, 32), ("parallel", 64, None, 16),
+                                                   ("parallel", 130, None, 64)])
+def test_edges_of_windows_and_pooled_blocks(kind, size, pool, dim, dtype):
+    cfg, w = needle_model(kind, size, pool, dim=dim)     # head sizes 32 and 64: the tensor-core prompt kernel
     at = 6
     edges = [at + size - 1, at + size]                          # the needle's last visible position, and the next
     if pool:

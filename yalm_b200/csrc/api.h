@@ -189,6 +189,17 @@ int yalm_attention_pooled(const void* q, const void* kv_step, const void* k_cach
                           const void* pool_k, const void* pool_v, int pool, int pool_capacity,
                           const int* pool_table, int pool_pps, int pool_pages, cudaStream_t stream);
 
+// Prefill attention with 32-bit softmax weights on tensor cores (attention_exact.cu; dtype 1 or 2,
+// head size 32, 64 or 128, window >= 0): S = Q K^T by mma.sync, softmax in 32 bits, P split into
+// three 16-bit terms for three P V products.  pool > 0: the pooled rows take part.
+int yalm_attention_exact_prefill(const void* q, const void* kv_step, const void* k_cache,
+                                 const void* v_cache, const int* q_start, const int* seq_slot,
+                                 const int* slot_pos, void* out, int dtype, int n_seqs, int max_q_len,
+                                 int H, int G, int hd, int capacity, int window, float scale,
+                                 const int* page_table, int pages_per_slot, int n_pages,
+                                 const void* pool_k, const void* pool_v, int pool, int pool_capacity,
+                                 const int* pool_table, int pool_pps, int pool_pages, cudaStream_t stream);
+
 // ---- qk_store.cu: after a q/k(/v) product with whole-projection norms and partial rotation ----
 // qkv: float32 slices [n_partials][tokens][(H + G (+ G)) hd] = (q | k | v, v only with has_v).
 // q_norm [H hd] / k_norm [G hd] (null: no norm): q <- q / sqrt(sum q^2 / n_q + eps) * q_norm over

@@ -96,6 +96,8 @@ _SIGNATURES = {
     "yalm_routed_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "yalm_attention_pooled": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                               _i, _i, _f, _i, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
+    "yalm_attention_exact_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
+                                     _f, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
     "yalm_qk_norm_rope_store": [_vp, _i, _ll, _vp, _vp, _i, _i, _f, _vp, _i, _i, _f, _vp, _vp, _vp, _vp,
                                 _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_pool_blocks": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i,
@@ -685,6 +687,36 @@ def residual_add(x: torch.Tensor, y: torch.Tensor, partials: Optional[torch.Tens
               and partials.numel() >= n_partials * x.numel(), "residual_add: partials")
     _check(lib().yalm_residual_add(_p(x), _p(y), _p(partials) if n_partials else None, n_partials,
                                    x.numel(), x.numel(), _stream()), "residual_add")
+
+
+def exact_attention_usable(dtype: torch.dtype, hd: int, chunk: Optional[int] = None) -> bool:
+    """The tensor-core prefill attention that keeps its softmax weights in 32 bits takes bfloat16 or
+    float16, head sizes 32, 64 and 128, and a sliding window or none (no chunked mask)."""
+    return dtype in HALF_TYPES and hd in (32, 64, 128) and not chunk
+
+
+def attention_exact_prefill(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
+                            v_cache: torch.Tensor, batch, slot_pos: torch.Tensor, out: torch.Tensor,
+                            H: int, G: int, hd: int, capacity: int, window: Optional[int], pages=None,
+                            scale: Optional[float] = None, pooled=None) -> None:
+    """Prefill attention on tensor cores with the weights split into three 16-bit terms (no
+    rounding of the softmax weights); ``pooled`` as in ``attention``."""
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
+    _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype and q.dtype in HALF_TYPES
+          and q.is_contiguous() and kv_step.is_contiguous() and out.is_contiguous(),
+          "attention_exact_prefill: one 16-bit type throughout")
+    pk = pv = ppt = None
+    pool = pcap = ppps = pnpg = 0
+    if pooled is not None:
+        pk, pv, pool, pcap, pool_pages = pooled
+        _need(bool(window) and pool > 0 and pk.dtype == pv.dtype == q.dtype,
+              "attention_exact_prefill: pooled rows go with a sliding window")
+        ppt, ppps, pnpg = _pages(pool_pages, pk, G, hd)
+    _check(lib().yalm_attention_exact_prefill(
+        _p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos),
+        _p(out), dtype_code(q.dtype), batch.n_seqs, max(batch.q_lens), H, G, hd, capacity, int(window or 0),
+        float(scale or 0.0), pt, pps, npg, _p(pk), _p(pv), int(pool), int(pcap), ppt, ppps, pnpg, _stream()),
+        "attention_exact_prefill")
 
 
 # ---- whole-projection norms, partial rotation, pooled blocks ----------------------------

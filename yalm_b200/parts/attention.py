@@ -330,7 +330,14 @@ class GQAAttention:
                                 pages=view.pages, pool_pages=pool_view.pages)
             pooled = (pool_view.k, pool_view.v, self.pool, pool_view.capacity, pool_view.pages)
         o = rt.buffer("attn_out", (n, H * hd), rt.dtype)
-        if self.pool or (self.exact and not batch.is_decode):
+        if ((self.pool or self.exact) and not batch.is_decode and rt.attention != "simt"
+                and ops.exact_attention_usable(rt.dtype, hd, self.chunk)):
+            # a prompt (or a portion of one): tensor cores with the softmax weights kept in 32 bits
+            # (three 16-bit terms per weight); the pooled rows are key blocks in front
+            ops.attention_exact_prefill(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
+                                        view.capacity, self.window, pages=view.pages, scale=self.scale,
+                                        pooled=pooled)
+        elif self.pool or (self.exact and not batch.is_decode):
             # 32-bit scores, weights and sums over the window's rows and the pooled rows; a decode
             # step's few queries are split over their keys so that the grid fills the device
             bound = max(1, batch.ctx_bound)
