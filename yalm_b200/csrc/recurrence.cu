@@ -91,13 +91,41 @@ recurrence_scan_kernel(const float* __restrict__ act, const int* __restrict__ q_
   pdl_wait();
   float S[RPT][RC_CPW];
   float* st = state + (((size_t)slot * H + h) * dk) * dv + col;
-#pragma unroll
-  for (int r = 0; r < RPT; ++r)
-#pragma unroll
-    for (int c = 0; c < RC_CPW; ++c) {
-      const int i = lane * RPT + r;
-      S[r][c] = (col + c < dv && i < dk) ? st[(size_t)i * dv + c] : 0.f;
+  // The block's part of the state is dk rows of RC_COLS neighbouring floats.  Where 16-byte
+  // accesses fit, it goes through shared memory (a warp reads eight whole 64-byte runs per load)
+  // instead of every lane picking its own rows out of memory 8 bytes at a time.
+  constexpr int TP = RC_COLS + 1;                     // tile pitch
+  const bool tiled = VEC == 4 && c0 + RC_COLS <= dv;
+  float* tile_g = state + (((size_t)slot * H + h) * dk) * dv + c0;
+  if (tiled) {
+    for (int i = threadIdx.x; i < dk * (RC_COLS / 4); i += blockDim.x) {
+      const int r = i / (RC_COLS / 4), q4 = i % (RC_COLS / 4);
+      const float4 v = *reinterpret_cast<const float4*>(tile_g + (size_t)r * dv + 4 * q4);
+      float* d = stage + r * TP + 4 * q4;
+      d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
     }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < RPT; ++r)
+#pragma unroll
+      for (int c = 0; c < RC_CPW; ++c) {
+        const int i = lane * RPT + r;
+        S[r][c] = i < dk ? stage[i * TP + w * RC_CPW + c] : 0.f;
+      }
+    __syncthreads();
+    if (dk < DKP) {                                   // the tile lay over rows that must read as zero
+      for (int i = threadIdx.x; i < dk * TP; i += blockDim.x) stage[i] = 0.f;
+      __syncthreads();
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < RPT; ++r)
+#pragma unroll
+      for (int c = 0; c < RC_CPW; ++c) {
+        const int i = lane * RPT + r;
+        S[r][c] = (col + c < dv && i < dk) ? st[(size_t)i * dv + c] : 0.f;
+      }
+  }
   const int n_groups = (t1 - t0 + RC_TOK - 1) / RC_TOK;
   auto issue = [&](int g) {
     if (g < n_groups) {
@@ -166,6 +194,23 @@ recurrence_scan_kernel(const float* __restrict__ act, const int* __restrict__ q_
     }
   }
   cp_async_wait<0>();
+  if (tiled) {
+    __syncthreads();                                   // the last group's rows are no longer read
+#pragma unroll
+    for (int r = 0; r < RPT; ++r)
+#pragma unroll
+      for (int c = 0; c < RC_CPW; ++c) {
+        const int i = lane * RPT + r;
+        if (i < dk) stage[i * TP + w * RC_CPW + c] = S[r][c];
+      }
+    __syncthreads();
+    for (int i = threadIdx.x; i < dk * (RC_COLS / 4); i += blockDim.x) {
+      const int r = i / (RC_COLS / 4), q4 = i % (RC_COLS / 4);
+      const float* d = stage + r * TP + 4 * q4;
+      *reinterpret_cast<float4*>(tile_g + (size_t)r * dv + 4 * q4) = make_float4(d[0], d[1], d[2], d[3]);
+    }
+    return;
+  }
 #pragma unroll
   for (int r = 0; r < RPT; ++r)
 #pragma unroll
