@@ -15,7 +15,8 @@
 
 namespace yalm {
 
-// One block per token.  The product's row is [q: H heads | k: G heads | v: G heads (if any)],
+// grid (token, part): every block of a token sums the whole row (the norms need it), and writes
+// its own part of the outputs; one part when there are many tokens.  The product's row is [q: H heads | k: G heads | v: G heads (if any)],
 // every head hd wide (rows beyond a head's true size are zero).  n_q / n_k: the true number of
 // features of q and k (what the mean of squares divides by).
 template <typename T>
@@ -59,8 +60,13 @@ __global__ void qk_norm_rope_store_kernel(
   if (k_norm != nullptr) rk = 1.0f / sqrtf(block_sum(ssk, scratch) / n_k + eps);
   __syncthreads();
   const int half = dims >> 1;
+  // this block's part of the outputs
+  const int per_part = (nq + nk + gridDim.y - 1) / gridDim.y;
+  const int i_lo = blockIdx.y * per_part, i_hi = min(nq + nk, i_lo + per_part);
+  const int v_per = (nk + gridDim.y - 1) / gridDim.y;
+  const int v_lo = blockIdx.y * v_per, v_hi = min(nk, v_lo + v_per);
   // q and k: norm, then rotate with the partner's normed value
-  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+  for (int i = i_lo + threadIdx.x; i < i_hi; i += blockDim.x) {
     const bool is_q = i < nq;
     const int j = is_q ? i : i - nq;                     // index inside q or k
     const int head = j / hd, e = j % hd;
@@ -89,7 +95,7 @@ __global__ void qk_norm_rope_store_kernel(
   }
   // values: the v rows, or the keys as they were projected
   const float* vs = row_s + nq + (has_v ? nk : 0);
-  for (int j = threadIdx.x; j < nk; j += blockDim.x) {
+  for (int j = v_lo + threadIdx.x; j < v_hi; j += blockDim.x) {
     const int head = j / hd, e = j % hd;
     const T val = from_float<T>(vs[j]);
     kv_step[((size_t)t * 2 * G + G + head) * hd + e] = val;
@@ -163,6 +169,13 @@ extern "C" int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long lo
   const size_t smem = (size_t)(((row + 1) & ~1) + dims) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   const int threads = row >= 2048 ? 512 : (row >= 512 ? 256 : 128);
+  // a few tokens (a decode step): several blocks per token, each with a part of the outputs
+  int parts = 1;
+  if (n_tokens < 74) {
+    parts = 148 / n_tokens;
+    if (parts > 8) parts = 8;
+    if (parts > row / 256) parts = row / 256 > 0 ? row / 256 : 1;
+  }
 #define YALM_QKS(T)                                                                                   \
   do {                                                                                                \
     static size_t attr = 48 * 1024;                                                                   \
@@ -172,7 +185,7 @@ extern "C" int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long lo
       if (e != cudaSuccess) return (int)e;                                                            \
       attr = smem;                                                                                    \
     }                                                                                                 \
-    launch_pdl(qk_norm_rope_store_kernel<T>, dim3(n_tokens), dim3(threads), smem, stream, qkv,        \
+    launch_pdl(qk_norm_rope_store_kernel<T>, dim3(n_tokens, parts), dim3(threads), smem, stream, qkv, \
                n_partials, partial_stride, q_norm, k_norm, (float)n_q, (float)n_k, eps, freq, dims,   \
                neighbours, mult, token_seq, q_start, seq_slot, slot_pos, (T*)q_out, (T*)kv_step,      \
                (T*)k_cache, (T*)v_cache, H, G, hd, has_v, capacity, write_cache, page_table,          \

@@ -22,7 +22,8 @@ constexpr int RC_COLS = 8 * RC_CPW;       // ... per block of eight warps
 constexpr int RC_TOK = 16;
 constexpr int RC_STAGES = 3;
 
-// One block per token; a thread walks the row with its own stride.
+// grid (token, part of the row): a thread takes four elements of the row, a block 1,024, so that
+// a decode step's few tokens still spread over many blocks.
 __global__ void recurrence_gates_kernel(const float* __restrict__ proj, int n_partials,
                                         long long partial_stride, const float* __restrict__ f_bias,
                                         const float* __restrict__ lower, float* __restrict__ act,
@@ -30,7 +31,8 @@ __global__ void recurrence_gates_kernel(const float* __restrict__ proj, int n_pa
   pdl_launch_dependents();
   pdl_wait();
   const size_t base = (size_t)blockIdx.x * row;
-  for (int e = threadIdx.x; e < row; e += blockDim.x) {
+  const int e_end = min(row, (int)(blockIdx.y + 1) * 1024);
+  for (int e = blockIdx.y * 1024 + threadIdx.x; e < e_end; e += blockDim.x) {
     const float z = sum_slices(proj + base + e, n_partials, partial_stride);
     float v = z;
     if (e < n_q) {
@@ -235,7 +237,8 @@ extern "C" int yalm_gated_recurrence(const float* proj, int n_partials, long lon
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
   if (H <= 0 || dk <= 0 || dv <= 0 || dk > 256 || n_seqs > 65535 || H > 65535) return -2;
   const int row = 2 * H * dk + H * dv;
-  launch_pdl(recurrence_gates_kernel, dim3(n_tokens), dim3(row >= 2048 ? 512 : 256), 0, stream, proj,
+  if ((row + 1023) / 1024 > 65535) return -4;
+  launch_pdl(recurrence_gates_kernel, dim3(n_tokens, (row + 1023) / 1024), dim3(256), 0, stream, proj,
              n_partials, partial_stride, f_bias, lower, act, row, H * dk);
   YALM_LAUNCH_CHECK();
   const dim3 grid((dv + RC_COLS - 1) / RC_COLS, H, n_seqs), block(256);
