@@ -361,7 +361,7 @@ def rudazen_config(width, heads, kv_heads, head_dim, window, pool, rot_dims, rec
     pooled = dict(att, mask={"size": window, "pool": pool}, rot={"base": 1e6, "dims": head_dim})
     left = dict(att, mask={"size": window},
                 rot={"base": 1e4, "dims": rot_dims,
-                     "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}})
+                     "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}})
     right = {"heads": rec_heads, "dim": rec_dim, "vdim": rec_vdim}
     mlp = {"kind": "dense", "ff": ff}
     layers = [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp} if c == "p" else
