@@ -395,3 +395,35 @@ def test_replay_program_on_a_model_folder(tmp_path, dtype):
     out = tmp_path / "out"
     os.makedirs(out)
     compare(tr, run_trace_run(str(folder), dtype, tr, str(out)), refs, cfg["vocab"], TOL[dtype])
+
+
+def test_command_line_on_a_random_model_folder(tmp_path):
+    """python -m yalm_b200: the random-weights mode writes a Rudazen model folder, greedy completion
+    of token-id prompts matches the plain implementation on the weights it wrote, and sampling with
+    a temperature repeats under one seed."""
+    import subprocess
+    import sys
+    from trace_tools import ROOT
+    from yalm_b200.weights import load_checkpoint
+    (tmp_path / "cfg.json").write_text(json.dumps(RUDA_A))
+    model = str(tmp_path / "model")
+    base = [sys.executable, "-m", "yalm_b200", model, "--dtype", "float32"]
+    r = subprocess.run(base + ["--random-weights", str(tmp_path / "cfg.json"), "--seed", "3",
+                               "--tokens", "5,6,7;9,10", "-n", "6", "-t", "0"],
+                       capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "Rudazen" in r.stdout and os.path.isfile(os.path.join(model, "model.safetensors"))
+    lines = [l for l in r.stdout.splitlines() if l.startswith("tokens:")]
+    assert len(lines) == 2
+    with open(os.path.join(model, "config.json")) as f:
+        cfg = json.load(f)
+    w = load_checkpoint(model)
+    for line, prompt in zip(lines, ([5, 6, 7], [9, 10])):
+        assert [int(t) for t in line.split("(")[0].split()[1:]] == plain_generate_greedy(cfg, w, prompt, 6)
+    sampled = []
+    for _ in range(2):
+        r = subprocess.run(base + ["--tokens", "5,6,7", "-n", "8", "-t", "0.9", "--seed", "11"],
+                           capture_output=True, text=True, cwd=ROOT, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        sampled.append([l for l in r.stdout.splitlines() if l.startswith("tokens:")])
+    assert sampled[0] == sampled[1] and sampled[0]
