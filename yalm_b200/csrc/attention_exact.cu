@@ -10,7 +10,7 @@
 //                  of the rounded form, and the result is that of 32-bit weights on 16-bit values.
 //
 // A block takes 64 query tokens of one head (four warps of 16 rows); keys come in blocks of 64
-// through shared memory.  A key is, in one numbering, a pooled block (one mean key / mean value
+// through two shared-memory buffers, the next block's cp.async copies under this block's products.  A key is, in one numbering, a pooled block (one mean key / mean value
 // row per `pool` positions that lie wholly before the query's window; see PoolArgs in
 // attention.cu), a position before this step (the cache ring) or a position of this step (the
 // step's own buffer).  Windows are sliding (window > 0) or none (0).
@@ -76,11 +76,13 @@ attn_exact_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kv_step
                           int capacity, int window, float scale_log2,
                           const int* __restrict__ page_table, int pps, int n_pages, ExactPool pl) {
   constexpr int LDS = HD + 8;                          // row pitch in elements: ldmatrix without bank conflicts
-  __shared__ __align__(16) T ks[EX_BK * LDS];
-  __shared__ __align__(16) T vs[EX_BK * LDS];
+  constexpr int TILE = EX_BK * LDS;                    // one block of keys (or values)
+  extern __shared__ __align__(16) uint8_t exact_smem[];      // two buffers of (K block, V block)
+  T* const bufs = reinterpret_cast<T*>(exact_smem);
   pdl_launch_dependents();
   pdl_wait();
-  const int b = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
+  // heads run fastest, the last (longest) query tiles of a sequence first: short blocks fill the tail
+  const int b = blockIdx.z, h = blockIdx.x, tile = gridDim.y - 1 - blockIdx.y;
   const int qs = q_start[b], ql = q_start[b + 1] - qs;
   if (tile * EX_BQ >= ql) return;
   const int slot = seq_slot[b];
@@ -113,38 +115,57 @@ attn_exact_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kv_step
   const int j_lo = first_visible(p_first, window);
   const int n_pool_blocks = (nb_max + EX_BK - 1) / EX_BK;
   const int n_tok_blocks = (p_last - j_lo + EX_BK) / EX_BK;
-  for (int kb = 0; kb < n_pool_blocks + n_tok_blocks; ++kb) {
+  const int n_blocks = n_pool_blocks + n_tok_blocks;
+  // a key block's rows into buffer (kb & 1): this thread copies half a row of K and of V in
+  // 16-byte cp.async pieces; rows beyond the range are filled with zeros (source size 0)
+  auto issue = [&](int kb) {
     const bool pooled = kb < n_pool_blocks;
     const int base = pooled ? kb * EX_BK : j_lo + (kb - n_pool_blocks) * EX_BK;
     const int limit = pooled ? nb_max : p_last + 1;
-    __syncthreads();                                   // the previous block's rows are no longer read
-    {
-      const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
-      const int key = base + row;
-      const T *kp = nullptr, *vp = nullptr;
-      if (key < limit) {
-        if (pooled) {
-          const size_t off = kv_row_offset(pl.table, pl.pps, pl.n_pages, slot, gkv, G, pl.capacity, key, HD);
-          kp = pool_k + off;
-          vp = pool_v + off;
-        } else if (key >= past) {
-          kp = kv_step + ((size_t)(qs + key - past) * 2 * G + gkv) * HD;
-          vp = kp + (size_t)G * HD;
-        } else {
-          const size_t off = kv_row_offset(page_table, pps, n_pages, slot, gkv, G, capacity, key % capacity, HD);
-          kp = k_cache + off;
-          vp = v_cache + off;
-        }
-      }
-      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-      for (int c = 0; c < HD / 16; ++c) {
-        const int e = half * (HD / 2) + c * 8;
-        *reinterpret_cast<uint4*>(ks + row * LDS + e) = kp ? *reinterpret_cast<const uint4*>(kp + e) : zero;
-        *reinterpret_cast<uint4*>(vs + row * LDS + e) = vp ? *reinterpret_cast<const uint4*>(vp + e) : zero;
+    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
+    const int key = base + row;
+    const T *kp = q, *vp = q;                          // any valid address when nothing is read
+    uint32_t bytes = 0;
+    if (key < limit) {
+      bytes = 16;
+      if (pooled) {
+        const size_t off = kv_row_offset(pl.table, pl.pps, pl.n_pages, slot, gkv, G, pl.capacity, key, HD);
+        kp = pool_k + off;
+        vp = pool_v + off;
+      } else if (key >= past) {
+        kp = kv_step + ((size_t)(qs + key - past) * 2 * G + gkv) * HD;
+        vp = kp + (size_t)G * HD;
+      } else {
+        const size_t off = kv_row_offset(page_table, pps, n_pages, slot, gkv, G, capacity, key % capacity, HD);
+        kp = k_cache + off;
+        vp = v_cache + off;
       }
     }
+    T* kd = bufs + (size_t)(kb & 1) * 2 * TILE + row * LDS;
+    T* vd = kd + TILE;
+#pragma unroll
+    for (int c = 0; c < HD / 16; ++c) {
+      const int e = half * (HD / 2) + c * 8;
+      const int se = bytes ? e : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(kd + e)), "l"(kp + se), "r"(bytes) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(vd + e)), "l"(vp + se), "r"(bytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (n_blocks > 0) issue(0);
+  for (int kb = 0; kb < n_blocks; ++kb) {
+    const bool pooled = kb < n_pool_blocks;
+    const int base = pooled ? kb * EX_BK : j_lo + (kb - n_pool_blocks) * EX_BK;
+    const int limit = pooled ? nb_max : p_last + 1;
+    if (kb + 1 < n_blocks) {                           // the next block's copies run under this block's products
+      issue(kb + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
+    const T* ks = bufs + (size_t)(kb & 1) * 2 * TILE;
+    const T* vs = ks + TILE;
 
     // ---- S = Q K^T: 16 rows x 64 keys per warp
     float s[8][4];
@@ -221,6 +242,7 @@ attn_exact_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kv_step
         Mma16<T>::run(o[2 * n2 + 1], hi, r[2], r[3]);
       }
     }
+    __syncthreads();                                   // this buffer is copied into again two blocks on
   }
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
@@ -257,16 +279,31 @@ extern "C" int yalm_attention_exact_prefill(const void* q, const void* kv_step, 
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (H > 65535 || n_seqs > 65535) return -4;
   const ExactPool pl = {pool_k, pool_v, pool_table, pool_pps, pool_pages, pool_capacity, pool > 0 ? pool : 0};
-  const dim3 grid((max_q_len + EX_BQ - 1) / EX_BQ, H, n_seqs), block(128);
+  const dim3 grid(H, (max_q_len + EX_BQ - 1) / EX_BQ, n_seqs), block(128);
+  if (grid.y > 65535) return -4;
+  const size_t smem = (size_t)2 * 2 * EX_BK * (hd + 8) * 2;
   const float scale_log2 = score_scale(scale, hd) * 1.4426950408889634f;
 #define YALM_EX(T, D)                                                                                \
-  launch_pdl(attn_exact_prefill_kernel<T, D>, grid, block, 0, stream, (const T*)q, (const T*)kv_step, \
-             (const T*)k_cache, (const T*)v_cache, q_start, seq_slot, slot_pos, (T*)out, H, G,        \
-             capacity, window, scale_log2, page_table, pages_per_slot, n_pages, pl)
+  do {                                                                                               \
+    static bool set = false;                                                                         \
+    if (!set && smem > 48 * 1024) {                                                                  \
+      cudaError_t e = cudaFuncSetAttribute(attn_exact_prefill_kernel<T, D>,                          \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+      if (e != cudaSuccess) return (int)e;                                                           \
+      set = true;                                                                                    \
+    }                                                                                                \
+    launch_pdl(attn_exact_prefill_kernel<T, D>, grid, block, smem, stream, (const T*)q,              \
+               (const T*)kv_step, (const T*)k_cache, (const T*)v_cache, q_start, seq_slot, slot_pos, \
+               (T*)out, H, G, capacity, window, scale_log2, page_table, pages_per_slot, n_pages, pl); \
+  } while (0)
   if (dtype == DT_BF16) {
-    if (hd == 32) YALM_EX(__nv_bfloat16, 32); else if (hd == 64) YALM_EX(__nv_bfloat16, 64); else YALM_EX(__nv_bfloat16, 128);
+    if (hd == 32) YALM_EX(__nv_bfloat16, 32);
+    else if (hd == 64) YALM_EX(__nv_bfloat16, 64);
+    else YALM_EX(__nv_bfloat16, 128);
   } else {
-    if (hd == 32) YALM_EX(__half, 32); else if (hd == 64) YALM_EX(__half, 64); else YALM_EX(__half, 128);
+    if (hd == 32) YALM_EX(__half, 32);
+    else if (hd == 64) YALM_EX(__half, 64);
+    else YALM_EX(__half, 128);
   }
 #undef YALM_EX
   YALM_LAUNCH_CHECK();
