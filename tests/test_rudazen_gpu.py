@@ -229,7 +229,7 @@ def test_tensor_core_attention_with_unrounded_weights(ops, hd, window, pool, dt)
     assert status.item() == 0
 
 
-@pytest.mark.parametrize("H, dk, dv", [(3, 24, 16), (1, 8, 40), (2, 20, 12), (2, 128, 64), (1, 200, 9), (2, 64, 128)])
+@pytest.mark.parametrize("H, dk, dv", [(3, 24, 16), (1, 8, 40), (2, 20, 12), (2, 128, 64), (1, 200, 9), (2, 64, 128), (1, 384, 24), (1, 301, 16)])
 def test_gated_recurrence_in_portions(ops, H, dk, dv):
     g = torch.Generator().manual_seed(dk)
     D = 32

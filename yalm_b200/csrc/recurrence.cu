@@ -76,11 +76,11 @@ recurrence_scan_kernel(const float* __restrict__ act, const int* __restrict__ q_
     for (int i = threadIdx.x; i < RC_STAGES * RC_TOK * PER_TOK; i += blockDim.x) stage[i] = 0.f;
     __syncthreads();
   }
-  // what this thread copies of every token: up to three runs of VEC floats
+  // what this thread copies of every token: up to five runs of VEC floats
   const int per = 2 * dk + RC_COLS;
-  int src_off[3], dst_off[3];
+  int src_off[5], dst_off[5];
 #pragma unroll
-  for (int k = 0; k < 3; ++k) {
+  for (int k = 0; k < 5; ++k) {
     const int e = (threadIdx.x + k * 256) * VEC;
     src_off[k] = dst_off[k] = -1;
     if (e < dk) { src_off[k] = h * dk + e; dst_off[k] = e; }
@@ -136,7 +136,7 @@ recurrence_scan_kernel(const float* __restrict__ act, const int* __restrict__ q_
       float* dst = stage + (size_t)(g % RC_STAGES) * RC_TOK * PER_TOK;
       const float* src = act + (size_t)base * row;
 #pragma unroll
-      for (int k = 0; k < 3; ++k)
+      for (int k = 0; k < 5; ++k)
         if (src_off[k] >= 0)
           for (int tt = 0; tt < nt; ++tt)
             cp_async<4 * VEC>(dst + tt * PER_TOK + dst_off[k], src + (size_t)tt * row + src_off[k]);
@@ -229,13 +229,13 @@ using namespace yalm;
 // proj: float32 slices [n_partials][tokens][2 H dk + H dv] = (q | f | v); f_bias, lower [H dk];
 // act: float32 scratch [tokens][2 H dk + H dv] (the activated projection); state
 // [slots][H][dk][dv] float32, read at the step's start and written at its end; out float32
-// [tokens][H dv].  dk up to 256.
+// [tokens][H dv].  dk up to 512.
 extern "C" int yalm_gated_recurrence(const float* proj, int n_partials, long long partial_stride,
                                      const float* f_bias, const float* lower, float* act,
                                      const int* q_start, const int* seq_slot, float* state, float* out,
                                      int n_tokens, int n_seqs, int H, int dk, int dv, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
-  if (H <= 0 || dk <= 0 || dv <= 0 || dk > 256 || n_seqs > 65535 || H > 65535) return -2;
+  if (H <= 0 || dk <= 0 || dv <= 0 || dk > 512 || n_seqs > 65535 || H > 65535) return -2;
   const int row = 2 * H * dk + H * dv;
   if ((row + 1023) / 1024 > 65535) return -4;
   launch_pdl(recurrence_gates_kernel, dim3(n_tokens, (row + 1023) / 1024), dim3(256), 0, stream, proj,
@@ -243,9 +243,9 @@ extern "C" int yalm_gated_recurrence(const float* proj, int n_partials, long lon
   YALM_LAUNCH_CHECK();
   const dim3 grid((dv + RC_COLS - 1) / RC_COLS, H, n_seqs), block(256);
   const int rpt = (dk + 31) / 32;
-  // 16-byte copies where every run starts on a 16-byte boundary; a thread copies up to three runs per token
+  // 16-byte copies where every run starts on a 16-byte boundary; a thread copies up to five runs per token
   const bool vec = dk % 4 == 0 && dv % 4 == 0 && (((uintptr_t)act) & 15) == 0;
-  if ((2 * dk + RC_COLS + (vec ? 3 : 0)) / (vec ? 4 : 1) > 3 * 256) return -2;
+  if ((2 * dk + RC_COLS + (vec ? 3 : 0)) / (vec ? 4 : 1) > 5 * 256) return -2;
 #define YALM_REC(R)                                                                                 \
   do {                                                                                              \
     const size_t smem = (size_t)RC_STAGES * RC_TOK * (2 * 32 * R + RC_COLS) * sizeof(float);        \
@@ -269,7 +269,8 @@ extern "C" int yalm_gated_recurrence(const float* proj, int n_partials, long lon
   if (rpt <= 1) YALM_REC(1);
   else if (rpt <= 2) YALM_REC(2);
   else if (rpt <= 4) YALM_REC(4);
-  else YALM_REC(8);
+  else if (rpt <= 8) YALM_REC(8);
+  else YALM_REC(16);
 #undef YALM_REC
   YALM_LAUNCH_CHECK();
   return 0;

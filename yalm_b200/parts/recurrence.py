@@ -30,8 +30,8 @@ class GatedLinearRecurrence:
         self.dk = int(params["key_dim"])
         self.dv = int(params["value_dim"])
         self.eps = float(params["eps"])
-        if min(self.H, self.dk, self.dv) <= 0 or self.dk > 256:
-            raise ValueError(f"gated_linear_recurrence: heads {self.H}, key size {self.dk} (up to 256), "
+        if min(self.H, self.dk, self.dv) <= 0 or self.dk > 512:
+            raise ValueError(f"gated_linear_recurrence: heads {self.H}, key size {self.dk} (up to 512), "
                              f"value size {self.dv}")
         self.w_qfv = self.w_o = self.f_bias = self.lower = self.norm = None
 
